@@ -1,0 +1,228 @@
+// Fused batched forward: conv 6x5x5 + bias + sigmoid, shared 4x4/stride-4 subsample + bias +
+// sigmoid, FC 216->10 + bias + sigmoid and argmax in ONE kernel.  Replaces, for n images at once,
+// the reference's forward_pass launch sequence (main.cu:67-88: 8 memsets, one H2D copy and nine
+// <<<64,64>>> launches per image) and classify's D2H + host argmax (main.cu:181-189).
+//
+// Data movement: images are contiguous 3,136-byte records, so a tile of 8 images is one 25 KB
+// 1-D bulk copy (cp.async.bulk, no multicast) into shared memory, double-buffered behind
+// mbarriers; the only other HBM traffic is the 44 bytes of results per image.
+//
+// Work decomposition: one thread owns one 4x4 subsample window (36 per image) for all six maps.
+// It keeps its 8x8 input patch in registers, so the 96 conv outputs, their sigmoids and the six
+// subsample outputs of the window never touch memory; only the 10 partial FC sums per window go
+// through shared memory, where 30 lanes per warp finish them and take the argmax by shuffles.
+#include "net.cuh"
+
+namespace cnn {
+
+constexpr int kFwImgs = 8;                  // images per tile
+constexpr int kFwThreads = kFwImgs * 36;    // 288 = 9 warps
+constexpr int kFwStages = 2;
+constexpr int kPartStride = 37;             // 36 windows + 1 pad: conflict-free column reads
+
+struct FwSmem {
+  float img[kFwStages][kFwImgs][kImg];      // 2 x 25,088 B, filled by bulk copies
+  float wc[kF][28];                         // 25 taps padded to 28 for 128-bit loads
+  float bc[8];
+  float ws[16];
+  float bs[4];
+  float wf[kOut][kS];                       // [k][f*36 + window]
+  float bf[12];
+  float part[kFwImgs][kOut][kPartStride];
+  unsigned long long full[kFwStages];
+};
+
+template <bool FAST, int MINB>
+__global__ void __launch_bounds__(kFwThreads, MINB)
+k_fused_forward(const float* __restrict__ images, long n, const float* __restrict__ params,
+                float* __restrict__ out, int* __restrict__ argmax, int* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  FwSmem& sm = *reinterpret_cast<FwSmem*>(smem_raw);
+  const int tid = threadIdx.x;
+  const long n_tiles = (n + kFwImgs - 1) / kFwImgs;
+
+  // Parameters: 9.4 KB from global (L2-resident after the first block) into shared memory.
+  for (int i = tid; i < kF * 28; i += kFwThreads) {
+    const int f = i / 28, t = i % 28;
+    sm.wc[f][t] = (t < 25) ? params[kOffWc + f * 25 + t] : 0.f;
+  }
+  if (tid < kF) sm.bc[tid] = params[kOffBc + tid];
+  if (tid < 16) sm.ws[tid] = params[kOffWs + tid];
+  if (tid == 0) sm.bs[0] = params[kOffBs];
+  for (int i = tid; i < kOut * kS; i += kFwThreads) sm.wf[i / kS][i % kS] = params[kOffWf + i];
+  if (tid < kOut) sm.bf[tid] = params[kOffBf + tid];
+
+  if (tid == 0) {
+    for (int s = 0; s < kFwStages; ++s) mbar_init(&sm.full[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  auto issue = [&](int stage, long tile) {
+    const long first = tile * kFwImgs;
+    const long left = n - first;
+    const unsigned cnt = (unsigned)(left < kFwImgs ? left : kFwImgs);
+    const unsigned bytes = cnt * (unsigned)(kImg * sizeof(float));
+    mbar_expect_tx(&sm.full[stage], bytes);
+    bulk_g2s(&sm.img[stage][0][0], images + first * kImg, bytes, &sm.full[stage]);
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < kFwStages; ++s) {
+      const long t = (long)blockIdx.x + (long)s * gridDim.x;
+      if (t < n_tiles) issue(s, t);
+    }
+  }
+
+  const int img = tid / 36, w = tid % 36;
+  const int p = w / 6, q = w % 6;
+  const int warp = tid >> 5, lane = tid & 31;
+  bool gave_up = false;
+
+  int it = 0;
+  for (long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+    const int stage = it % kFwStages;
+    const unsigned parity = (unsigned)(it / kFwStages) & 1u;
+    mbar_wait_bounded(&sm.full[stage], parity, status, gave_up);
+
+    const long first = tile * kFwImgs;
+    const int imgs_here = (int)((n - first) < kFwImgs ? (n - first) : kFwImgs);
+    const bool live = img < imgs_here;
+
+    // 8x8 input patch of this thread's window: rows 4p..4p+7, columns 4q..4q+7.
+    float patch[8][8];
+    if (live) {
+      const float* base = &sm.img[stage][img][(4 * p) * kH + 4 * q];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 lo = *reinterpret_cast<const float4*>(base + r * kH);
+        const float4 hi = *reinterpret_cast<const float4*>(base + r * kH + 4);
+        patch[r][0] = lo.x; patch[r][1] = lo.y; patch[r][2] = lo.z; patch[r][3] = lo.w;
+        patch[r][4] = hi.x; patch[r][5] = hi.y; patch[r][6] = hi.z; patch[r][7] = hi.w;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) patch[r][c] = 0.f;
+    }
+    __syncthreads();  // every thread has taken its patch: the stage may be refilled
+    if (tid == 0) {
+      const long t2 = tile + (long)kFwStages * gridDim.x;
+      if (t2 < n_tiles) issue(stage, t2);
+    }
+
+    float part[kOut];
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) part[k] = 0.f;
+
+#pragma unroll 1
+    for (int f = 0; f < kF; ++f) {
+      float wr[28];
+#pragma unroll
+      for (int t = 0; t < 7; ++t) {
+        const float4 v = *reinterpret_cast<const float4*>(&sm.wc[f][4 * t]);
+        wr[4 * t] = v.x; wr[4 * t + 1] = v.y; wr[4 * t + 2] = v.z; wr[4 * t + 3] = v.w;
+      }
+      const float b = sm.bc[f];
+      float a[4][4];
+#pragma unroll
+      for (int y = 0; y < 4; ++y)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < 5; ++j)
+#pragma unroll
+            for (int i = 0; i < 5; ++i) acc = fmaf(wr[i * 5 + j], patch[y + i][x + j], acc);
+          a[y][x] = sigmoidf<FAST>(acc + b);
+        }
+      float zs = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) zs = fmaf(sm.ws[i * 4 + j], a[i][j], zs);
+      const float as = sigmoidf<FAST>(zs + sm.bs[0]);
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) part[k] = fmaf(sm.wf[k][f * 36 + w], as, part[k]);
+    }
+
+    if (live) {
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) sm.part[img][k][w] = part[k];
+    }
+    __syncthreads();
+
+    // Three images per warp on lanes 0..29: lane = 10*local_image + k.
+    if (warp < 3) {
+      const int li = lane / 10, k = lane % 10;
+      const int im = warp * 3 + li;
+      const bool valid = (lane < 30) && (im < imgs_here);
+      float z = 0.f;
+      if (valid) {
+#pragma unroll 4
+        for (int ww = 0; ww < 36; ++ww) z += sm.part[im][k][ww];
+        z += sm.bf[k];
+      }
+      const float o = sigmoidf<FAST>(z);
+      // classify(): strict '<' scan from index 0, so the lowest index wins ties.
+      float bv = __shfl_sync(0xffffffffu, o, li * 10);
+      int best = 0;
+#pragma unroll
+      for (int kk = 1; kk < kOut; ++kk) {
+        const float v = __shfl_sync(0xffffffffu, o, li * 10 + kk);
+        if (bv < v) { bv = v; best = kk; }
+      }
+      if (valid) {
+        const long gi = first + im;
+        if (out) out[gi * kOut + k] = o;
+        if (argmax && k == 0) argmax[gi] = best;
+      }
+    }
+  }
+}
+
+template <bool FAST, int MINB>
+static int launch_variant(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+                          cudaStream_t stream) {
+  const long n_tiles = (n + kFwImgs - 1) / kFwImgs;
+  const long max_blocks = (long)MINB * sm_count();
+  const int grid = (int)(n_tiles < max_blocks ? n_tiles : max_blocks);
+  const size_t smem = sizeof(FwSmem);
+  CNN_CUDA(cudaFuncSetAttribute(k_fused_forward<FAST, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)smem));
+  k_fused_forward<FAST, MINB><<<grid, kFwThreads, smem, stream>>>(d_images, n, net->d_params, d_out,
+                                                                 d_argmax, net->d_status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "k_fused_forward launch");
+  return CNN_OK;
+}
+
+// fw_variant: 0 = two blocks per SM (register-capped), 1 = one block per SM (no cap).
+static int launch_forward(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+                          cudaStream_t stream) {
+  if (net->fw_variant == 1) {
+    return net->fast_sigmoid ? launch_variant<true, 1>(net, d_images, n, d_out, d_argmax, stream)
+                             : launch_variant<false, 1>(net, d_images, n, d_out, d_argmax, stream);
+  }
+  return net->fast_sigmoid ? launch_variant<true, 2>(net, d_images, n, d_out, d_argmax, stream)
+                           : launch_variant<false, 2>(net, d_images, n, d_out, d_argmax, stream);
+}
+
+int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+                   cudaStream_t stream) {
+  return launch_forward(net, d_images, n, d_out, d_argmax, stream);
+}
+
+}  // namespace cnn
+
+extern "C" int cnn_forward_batched(cnn_net* net, const float* d_images, long n, float* d_out,
+                                   int* d_argmax, void* stream) {
+  CNN_REQUIRE(net != nullptr, "cnn_forward_batched: NULL net");
+  CNN_REQUIRE(n >= 0, "cnn_forward_batched: negative image count");
+  if (n == 0) return CNN_OK;
+  CNN_REQUIRE(d_images != nullptr, "cnn_forward_batched: NULL images");
+  CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
+              "cnn_forward_batched: image batch must start on a 16-byte boundary");
+  return cnn::forward_device(net, d_images, n, d_out, d_argmax, cnn::as_stream(stream));
+}

@@ -1,0 +1,83 @@
+// The fused-network handle shared by the forward, training and host-pipeline translation units.
+#pragma once
+
+#include "cnn_common.cuh"
+
+struct cnn_net {
+  int device = 0;
+  float* d_params = nullptr;       // kNParamsPadded floats
+  int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out
+  int fast_sigmoid = 0;
+  int fw_variant = 0;              // forward kernel variant (tuning knob, see cnn_net_set_option)
+
+  // Training scratch (allocated on first use): per-block partial gradients and the reduced vector.
+  float* d_partials = nullptr;     // [partial_rows][kNParamsPadded]
+  int partial_rows = 0;
+  float* d_grad = nullptr;         // kNParamsPadded floats + 8 floats of statistics
+  // Host pipeline staging (allocated on first use).
+  float* d_stage_img[2] = {nullptr, nullptr};
+  float* d_stage_out[2] = {nullptr, nullptr};
+  int* d_stage_arg[2] = {nullptr, nullptr};
+  long stage_images = 0;
+  cudaStream_t copy_stream[2] = {nullptr, nullptr};
+  cudaEvent_t stage_done[2] = {nullptr, nullptr};
+};
+
+namespace cnn {
+
+// ---- mbarrier / bulk-copy primitives (sm_90+ PTX, used in their non-multicast form only) ----
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// 1-D bulk copy global -> this CTA's shared memory, completion signalled on an mbarrier.
+// Both addresses must be 16-byte aligned and bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes,
+                                         unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after about two seconds of SM clocks, records it in *status and lets the
+// caller carry on (with whatever the buffer holds) so that control flow stays uniform and the
+// kernel always terminates.  Returns false once a wait has run out.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity,
+                                                  int* status, bool& gave_up) {
+  if (gave_up) return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > 4000000000LL) {
+      gave_up = true;
+      if (status) atomicExch(status, 1);
+      return false;
+    }
+  }
+  return true;
+}
+
+int ensure_train_scratch(cnn_net* net, int rows);
+
+}  // namespace cnn

@@ -1,0 +1,198 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of the reference CNN hot path:
+ *   28x28 input -> conv 6x5x5 (valid) -> sigmoid -> one shared 4x4/stride-4 weighted subsample
+ *   -> sigmoid -> fully connected 216->10 -> sigmoid, with the reference's per-sample SGD rule.
+ *
+ * The reference has no FFI layer: its boundary is the C++/CUDA header layer.h (class Layer plus
+ * 19 __global__ kernels launched by the caller).  This header is what a binding for that path
+ * would import instead; every entry point names the reference interface it replaces.  A C++
+ * source-level drop-in with the reference's own names (class Layer, fp_*, bp_*, ...) lives in
+ * the package's compat/layer.h.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative cnn_status; nothing throws or aborts;
+ *     cnn_last_error() returns a thread-local description of the most recent failure;
+ *   - pointers named d_* are device pointers, h_* are host pointers; "stream" is a cudaStream_t
+ *     passed as void* (NULL = the legacy default stream, as the reference uses);
+ *   - all tensors are fp32, row-major, contiguous; image batches are [n][28][28] and must start
+ *     on a 16-byte boundary;
+ *   - parameter arena order (2343 floats): [Wc 150 | bc 6 | Ws 16 | bs 1 | Wf 2160 | bf 10], each
+ *     block in the reference's Layer::weight / Layer::bias layout (layer.cu:19-27);
+ *   - there is no CPU fallback: without a usable CUDA device every compute call fails.
+ */
+#ifndef CNN_B200_H
+#define CNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum cnn_status {
+  CNN_OK = 0,
+  CNN_ERR_INVALID = -1,   /* bad argument (NULL pointer, negative size, misaligned batch) */
+  CNN_ERR_CUDA = -2,      /* a CUDA runtime call or launch failed; see cnn_last_error() */
+  CNN_ERR_TIMEOUT = -3,   /* a bounded device-side wait ran out (reported, never hangs) */
+  CNN_ERR_UNSUPPORTED = -4/* shape or mode this build does not implement */
+} cnn_status;
+
+#define CNN_N_PARAMS 2343
+#define CNN_IMAGE_ELEMS 784
+#define CNN_N_OUT 10
+
+const char* cnn_last_error(void);
+/* Library version and the -gencode target it was compiled for, e.g. "sm_100a". */
+const char* cnn_build_info(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Layer object -- replaces class Layer (layer.h:14-35).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct cnn_layer cnn_layer;
+
+/* Device buffers of a layer, same names as the reference's public members (layer.h:18-26). */
+typedef struct cnn_layer_view {
+  int M, N, O;
+  float* output;   /* [O]   */
+  float* preact;   /* [O]   */
+  float* bias;     /* [N]   */
+  float* weight;   /* [N*M] */
+  float* d_output; /* [O]   */
+  float* d_preact; /* [O]   */
+  float* d_weight; /* [N*M] */
+} cnn_layer_view;
+
+/* Layer::Layer(M,N,O), layer.cu:5-43: allocates the seven buffers and fills bias[i], then
+ * weight[i*M..] for each unit i with 0.5f - rand()/RAND_MAX from the C library's rand(), in the
+ * reference's draw order. */
+int cnn_layer_create(int M, int N, int O, cnn_layer** out);
+/* Layer::~Layer, layer.cu:46-58. */
+int cnn_layer_destroy(cnn_layer* l);
+/* Layer::setOutput, layer.cu:61-64: blocking copy of O host floats into output. */
+int cnn_layer_set_output(cnn_layer* l, const float* h_data);
+/* Layer::clear, layer.cu:67-71: zero output and preact. */
+int cnn_layer_clear(cnn_layer* l);
+/* Layer::bp_clear, layer.cu:73-78: zero d_output, d_preact, d_weight. */
+int cnn_layer_bp_clear(cnn_layer* l);
+/* Exposes the public data members of layer.h:16-26. */
+int cnn_layer_view_get(const cnn_layer* l, cnn_layer_view* out);
+
+/* ------------------------------------------------------------------------------------------
+ * Per-operator launchers -- one per reference kernel, same argument order as layer.h:40-62.
+ * Each keeps the reference's contract: accumulate-into-existing-contents where the reference
+ * uses atomicAdd, in-place "+=" for the bias kernels and apply_grad, plain stores elsewhere.
+ * None uses atomics: every output element is owned by one thread (or one warp), so results are
+ * bit-reproducible run to run.
+ * ---------------------------------------------------------------------------------------- */
+int cnn_apply_step_function(const float* d_input, float* d_output, int n, void* stream); /* layer.cu:86-94 */
+int cnn_make_error(float* d_err, const float* d_output, unsigned int label, int n, void* stream); /* layer.cu:96-104 */
+int cnn_apply_grad(float* d_output, const float* d_grad, int n, void* stream);           /* layer.cu:106-114 */
+
+int cnn_fp_preact_c1(const float* d_input, float* d_preact, const float* d_weight, void* stream); /* layer.cu:116-133 */
+int cnn_fp_bias_c1(float* d_preact, const float* d_bias, void* stream);                           /* layer.cu:135-150 */
+int cnn_fp_preact_s1(const float* d_input, float* d_preact, const float* d_weight, void* stream); /* layer.cu:152-169 */
+int cnn_fp_bias_s1(float* d_preact, const float* d_bias, void* stream);                           /* layer.cu:171-186 */
+int cnn_fp_preact_f(const float* d_input, float* d_preact, const float* d_weight, void* stream);  /* layer.cu:188-204 */
+int cnn_fp_bias_f(float* d_preact, const float* d_bias, void* stream);                            /* layer.cu:206-216 */
+
+int cnn_bp_weight_f(float* d_d_weight, const float* d_d_preact, const float* d_p_output, void* stream);  /* layer.cu:218-234 */
+int cnn_bp_bias_f(float* d_bias, const float* d_d_preact, void* stream);                                 /* layer.cu:236-246 */
+int cnn_bp_output_s1(float* d_d_output, const float* d_n_weight, const float* d_nd_preact, void* stream);/* layer.cu:248-264 */
+int cnn_bp_preact_s1(float* d_d_preact, const float* d_d_output, const float* d_preact, void* stream);   /* layer.cu:266-283 */
+int cnn_bp_weight_s1(float* d_d_weight, const float* d_d_preact, const float* d_p_output, void* stream); /* layer.cu:285-304 */
+int cnn_bp_bias_s1(float* d_bias, const float* d_d_preact, void* stream);                                /* layer.cu:306-322 */
+int cnn_bp_output_c1(float* d_d_output, const float* d_n_weight, const float* d_nd_preact, void* stream);/* layer.cu:324-342 */
+int cnn_bp_preact_c1(float* d_d_preact, const float* d_d_output, const float* d_preact, void* stream);   /* layer.cu:344-361 */
+int cnn_bp_weight_c1(float* d_d_weight, const float* d_d_preact, const float* d_p_output, void* stream); /* layer.cu:363-381 */
+int cnn_bp_bias_c1(float* d_bias, const float* d_d_preact, void* stream);                                /* layer.cu:383-399 */
+
+/* ------------------------------------------------------------------------------------------
+ * Fused network -- replaces the launch sequences that ARE the reference's model:
+ * forward_pass (main.cu:55-92), back_pass (main.cu:95-123), learn (125-170), classify/test
+ * (173-208), with the four Layer globals of main.cu:17-20 as one parameter arena.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct cnn_net cnn_net;
+
+/* Creates the net on the current CUDA device.  Parameters are drawn like the reference's static
+ * Layer objects would draw them after srand(seed) (c1, s1, f in that order; main.cu:17-20), so
+ * seed 0 or 1 gives the reference binary's own initial parameters. */
+int cnn_net_create(unsigned int seed, cnn_net** out);
+int cnn_net_destroy(cnn_net* net);
+/* Blocking copies of the 2343-float arena from / to host memory. */
+int cnn_net_set_params(cnn_net* net, const float* h_params);
+int cnn_net_get_params(cnn_net* net, float* h_params);
+/* Device pointer of the arena (CNN_N_PARAMS floats, padded to 2368), for collectives. */
+int cnn_net_params_device(cnn_net* net, float** d_params);
+
+/* Sigmoid flavour of the fused kernels: 0 = the reference's own expression 1/(1+expf(-v)) with
+ * IEEE division (layer.cu:81-84), bit-identical to the reference for equal pre-activations;
+ * 1 = ex2.approx / rcp.approx based, about 1e-6 relative from it.  Default 0. */
+int cnn_net_set_fast_sigmoid(cnn_net* net, int enable);
+
+/* Synchronises the device and reports whether any kernel of this net gave up a bounded wait since
+ * the last call (CNN_ERR_TIMEOUT, *status non-zero); the status word is cleared. */
+int cnn_net_status(cnn_net* net, int* status);
+
+/* Batched forward (forward_pass + classify for n images at once): d_images [n][28][28] ->
+ * d_out [n][10] sigmoids and d_argmax [n] (lowest index wins ties, main.cu:183-189).  Either
+ * output may be NULL.  One fused kernel; activations never leave the chip. */
+int cnn_forward_batched(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+                        void* stream);
+
+/* Same through host buffers: pipelined pinned-or-pageable H2D of the images in chunks, the fused
+ * kernel per chunk, D2H of the results; returns after everything has landed. */
+int cnn_forward_batched_host(cnn_net* net, const float* h_images, long n, float* h_out,
+                             int* h_argmax);
+
+/* Device-side synthetic data (stands in for the MNIST files the reference reads, main.cu:30-33):
+ * image i of the set 'seed' = strokes of uint8 values 128..255 on a zero canvas, stored as
+ * float(uint8)/255 like mnist.h:145; label = hash % 10.  Bit-identical to the host generator in
+ * the Python package.  d_labels may be NULL. */
+int cnn_synth_images(unsigned long long seed, long first_index, long n, float* d_images,
+                     unsigned int* d_labels, void* stream);
+
+/* Tuning knobs, by name: "fw_variant" (0 = two blocks per SM with a register cap, 1 = one block per
+ * SM), "fast_sigmoid" (as cnn_net_set_fast_sigmoid). */
+int cnn_net_set_option(cnn_net* net, const char* key, int value);
+
+/* ------------------------------------------------------------------------------------------
+ * Training.  The "gradient" of one image is what one reference step would add to each parameter,
+ * divided by dt: the d_weight buffers for weights (bp_weight_f / bp_weight_s1 / bp_weight_c1,
+ * layer.cu:218-234, 285-304, 363-381), and for biases delta_f[k], sum(delta_s)/216 and
+ * sum(delta_c[f])/576 (bp_bias_f / bp_bias_s1 / bp_bias_c1, layer.cu:236-246, 306-322, 383-399).
+ * With a batch of one, params += dt * gradient is the reference's step.
+ * ---------------------------------------------------------------------------------------- */
+
+/* forward_pass + makeError + back_pass (main.cu:55-123, 147-153) for n images at FIXED parameters:
+ * d_grad[0..2342] = sum of the per-image gradients (arena order), d_grad[2344] = sum of the
+ * per-image error norms ||delta_f||_2 (what cublasSnrm2 returns at main.cu:153); the rest of the
+ * 2368 floats is zero.  Uses the net's scratch rows; deterministic (no atomics). */
+int cnn_grad_batch(cnn_net* net, const float* d_images, const unsigned int* d_labels, long n,
+                   float* d_grad, void* stream);
+/* apply_grad for the whole arena (layer.cu:106-114 with a caller-chosen step):
+ * params[i] += scale * d_grad[i], i < 2343. */
+int cnn_apply_update(cnn_net* net, const float* d_grad, float scale, void* stream);
+
+/* Minibatch SGD over n images in index order: for each batch of `batch` images (the last one may
+ * be smaller) params += (dt / batch_size) * sum of gradients.  d_mean_err (device, `epochs`
+ * floats, may be NULL) receives the per-epoch mean error norm.  Asynchronous on `stream`. */
+int cnn_train_minibatch(cnn_net* net, const float* d_images, const unsigned int* d_labels, long n,
+                        int batch, int epochs, float dt, float* d_mean_err, void* stream);
+
+/* learn() (main.cu:125-170): per-sample SGD in index order, one step per image, in one persistent
+ * kernel; after each epoch the mean error norm goes to h_mean_err[epoch] and training stops early
+ * when it is below `threshold` (the reference uses 0.01; pass a negative value to disable).
+ * Blocking; *h_epochs_run receives the number of epochs run. */
+int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned int* d_labels, long n,
+                            int epochs, float dt, float threshold, float* h_mean_err, int* h_epochs_run,
+                            void* stream);
+
+/* Blocking copies between host and device memory (for bindings without a CUDA runtime of their own). */
+int cnn_copy_to_host(void* h_dst, const void* d_src, size_t bytes);
+int cnn_copy_to_device(void* d_dst, const void* h_src, size_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CNN_B200_H */
