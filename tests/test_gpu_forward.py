@@ -1,0 +1,156 @@
+"""Fused batched forward (GPU) against the oracle, the reference kernels and itself."""
+import numpy as np
+import pytest
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def run_forward(torch, net, images, want_out=True, want_arg=True, offset_elems=0):
+    n = images.shape[0]
+    flat = torch.zeros(n * 784 + offset_elems + 4, dtype=torch.float32, device="cuda")
+    d_img = flat[offset_elems:offset_elems + n * 784]
+    if n:
+        d_img.copy_(torch.from_numpy(np.ascontiguousarray(images).reshape(-1)))
+    d_out = torch.full((n, 10), -1.0, dtype=torch.float32, device="cuda") if want_out else None
+    d_arg = torch.full((n,), -1, dtype=torch.int32, device="cuda") if want_arg else None
+    net.forward(d_img, n, d_out, d_arg)
+    torch.cuda.synchronize()
+    assert net.status() == 0
+    return (d_out.cpu().numpy() if want_out else None), (d_arg.cpu().numpy() if want_arg else None)
+
+
+def clear_margin(out, tol=1e-5):
+    top2 = np.sort(out, axis=1)
+    return (top2[:, -1] - top2[:, -2]) > tol * top2[:, -1]
+
+
+@pytest.mark.parametrize("fast", [False, True])
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 100, 2368 + 5, 4099])
+def test_forward_matches_oracle(cuda, pkg, ob, params0, n, fast, variant):
+    images, _ = pkg.synth.synth_images(21, n)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.set_fast_sigmoid(fast)
+    net.set_option("fw_variant", variant)
+    out, arg = run_forward(cuda, net, images)
+    ref_out, ref_arg = ob.forward_batch(params0, images)
+    assert rel_err(out, ref_out) < 1e-5       # the 1e-5 relative bar on activations
+    ok = clear_margin(ref_out)
+    assert np.array_equal(arg[ok], ref_arg[ok])
+    # the argmax written by the kernel is the lowest-index maximum of the row it wrote
+    assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
+
+
+def test_forward_empty_and_optional_outputs(cuda, pkg, ob, params0):
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.forward(None, 0, None, None)
+    images, _ = pkg.synth.synth_images(22, 50)
+    out, _ = run_forward(cuda, net, images, want_arg=False)
+    _, arg = run_forward(cuda, net, images, want_out=False)
+    assert np.array_equal(arg, np.argmax(out, axis=1))
+
+
+def test_forward_rejects_bad_arguments(cuda, pkg, params0):
+    net = pkg.Net(0)
+    d = cuda.zeros(784 * 4 + 8, dtype=cuda.float32, device="cuda")
+    with pytest.raises(pkg.CnnError) as e:
+        net.forward(d[1:], 2, None, None)   # 4-byte offset: not 16-byte aligned
+    assert e.value.code == -1 and "16-byte" in str(e.value)
+    with pytest.raises(pkg.CnnError):
+        net.forward(d, -1, None, None)
+    with pytest.raises(pkg.CnnError):
+        net.forward(None, 3, None, None)
+    # a 16-byte (4-float) offset is fine
+    net.forward(d[4:], 2, None, None)
+    cuda.cuda.synchronize()
+
+
+def test_forward_is_deterministic_and_tie_breaks_low(cuda, pkg, params0):
+    images, _ = pkg.synth.synth_images(23, 1000)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    a = run_forward(cuda, net, images)
+    b = run_forward(cuda, net, images)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    # all-zero FC weights and equal biases: every output equal, index 0 must win
+    p = params0.copy()
+    p[173:2333] = 0
+    p[2333:] = 0.25
+    net.set_params(p)
+    out, arg = run_forward(cuda, net, images[:20])
+    assert np.all(out == out[0, 0]) and np.all(arg == 0)
+
+
+def test_forward_host_pipeline(cuda, pkg, ob, params0):
+    n = 8192 * 2 + 123          # spans three staging chunks
+    images, _ = pkg.synth.synth_images(24, n)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    h_img = cuda.from_numpy(images).pin_memory()
+    h_out = cuda.empty((n, 10), dtype=cuda.float32).pin_memory()
+    h_arg = cuda.empty((n,), dtype=cuda.int32).pin_memory()
+    net.forward_host(h_img, n, h_out, h_arg)
+    d_out, d_arg = run_forward(cuda, net, images)
+    assert np.array_equal(h_out.numpy(), d_out) and np.array_equal(h_arg.numpy(), d_arg)
+    # pageable host memory works too
+    out2 = np.empty((n, 10), dtype=np.float32)
+    net.forward_host(images, n, out2, None)
+    assert np.array_equal(out2, d_out)
+
+
+def test_forward_against_reference_kernels(cuda, pkg, ob, params0):
+    if not ob.reference_available():
+        pytest.skip("reference kernels not built")
+    images, _ = pkg.synth.synth_images(25, 96)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    out, arg = run_forward(cuda, net, images)
+    ref = ob.Reference(0)
+    ref.set_params(params0)
+    ref_out = np.zeros((96, 10), dtype=np.float32)
+    ref_arg = np.zeros(96, dtype=np.int32)
+    for i in range(96):
+        ref_arg[i] = ref.classify(images[i])
+        ref_out[i] = ref.read("f", "output")
+    ref.close()
+    assert rel_err(out, ref_out) < 1e-5
+    ok = clear_margin(ref_out)
+    assert np.array_equal(arg[ok], ref_arg[ok])
+
+
+def test_full_size_property_linearity_in_batch(cuda, pkg, params0):
+    """BASELINE config 2 size (65,536 images): results of a batch do not depend on where an image
+    sits in it -- the full batch equals the concatenation of two half batches, bit for bit, and the
+    device generator fills the same images as the host generator."""
+    n = 65536
+    net = pkg.Net(0)
+    net.set_params(params0)
+    d_img = cuda.empty((n, 28, 28), dtype=cuda.float32, device="cuda")
+    pkg.synth_images_device(1, 0, n, d_img)
+    d_out = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
+    d_arg = cuda.empty((n,), dtype=cuda.int32, device="cuda")
+    net.forward(d_img, n, d_out, d_arg)
+    o2 = cuda.empty_like(d_out)
+    a2 = cuda.empty_like(d_arg)
+    half = n // 2 + 3 * 8       # keeps the second half on a tile boundary multiple
+    net.forward(d_img, half, o2, a2)
+    net.forward(d_img[half:], n - half, o2[half:], a2[half:])
+    cuda.cuda.synchronize()
+    assert cuda.equal(d_out, o2) and cuda.equal(d_arg, a2)
+    host, _ = pkg.synth.synth_images(1, 2048, first_index=30000)
+    assert np.array_equal(d_img[30000:32048].cpu().numpy(), host)
+
+
+def test_device_generator_matches_host(cuda, pkg):
+    n = 3000
+    d_img = cuda.empty((n, 28, 28), dtype=cuda.float32, device="cuda")
+    d_lab = cuda.empty((n,), dtype=cuda.int32, device="cuda")
+    pkg.synth_images_device(9, 12345, n, d_img, d_lab)
+    cuda.cuda.synchronize()
+    h_img, h_lab = pkg.synth.synth_images(9, n, first_index=12345)
+    assert np.array_equal(d_img.cpu().numpy(), h_img)
+    assert np.array_equal(d_lab.cpu().numpy().astype(np.uint32), h_lab)
