@@ -305,8 +305,11 @@ class Net:
         _check(load_library().cnn_net_params_device(self._h, C.byref(p)))
         return int(p.value)
 
-    def set_fast_sigmoid(self, enable: bool) -> None:
-        _check(load_library().cnn_net_set_fast_sigmoid(self._h, 1 if enable else 0))
+    def set_fast_sigmoid(self, flavour) -> None:
+        """Sigmoid flavour of the fused kernels: 0/False = the reference expression, 1/True =
+        ex2/rcp approximations (about 1e-6 relative), 2 = reduced-argument ex2 + refined reciprocal
+        (a few 1e-7 relative)."""
+        _check(load_library().cnn_net_set_fast_sigmoid(self._h, int(flavour)))
 
     def set_option(self, key: str, value: int) -> None:
         _check(load_library().cnn_net_set_option(self._h, key.encode(), int(value)))

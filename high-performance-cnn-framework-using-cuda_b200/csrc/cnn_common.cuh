@@ -33,12 +33,38 @@ constexpr int kNParamsPadded = 2368;  // multiple of 32 floats
 
 constexpr float kDt = 1.0e-1f;  // layer.h:11
 
-// step_function, layer.cu:81-84.  The exact flavour is the reference's own expression, compiled
-// without fast-math, so equal pre-activations give bit-equal activations.
-template <bool FAST>
+__device__ __forceinline__ float exp2f_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// step_function, layer.cu:81-84.  Three flavours, selected at compile time:
+//   0  the reference's own expression, compiled without fast-math (libdevice expf, IEEE divide):
+//      equal pre-activations give bit-equal activations;
+//   1  __expf and __fdividef (ex2.approx / rcp.approx based): about 1e-6 relative from flavour 0
+//      for |v| <= 16 (the multiplication by log2e is rounded before the exponential);
+//   2  same two special-function instructions, but with the argument reduced in two FMA steps
+//      (n = round(-v*log2e), r = -v - n*ln2 exactly) and one Newton step on the reciprocal:
+//      about 12 instructions, within a few 1e-7 relative of flavour 0.
+template <int FLAVOR>
 __device__ __forceinline__ float sigmoidf(float v) {
-  if constexpr (FAST) {
+  if constexpr (FLAVOR == 1) {
     return __fdividef(1.0f, 1.0f + __expf(-v));
+  } else if constexpr (FLAVOR == 2) {
+    const float x = fminf(fmaxf(-v, -87.0f), 87.0f);
+    const float magic = 12582912.0f;                       // 1.5 * 2^23: adding it rounds to integer
+    const float t = fmaf(x, 1.4426950408889634f, magic);
+    const float n = t - magic;                              // round(x * log2e)
+    float r = fmaf(n, -0.693145751953125f, x);              // x - n*ln2_hi (exact)
+    r = fmaf(n, -1.4286068203094173e-6f, r);                // ... - n*ln2_lo
+    const float m = exp2f_approx(r * 1.4426950408889634f);  // 2^(r*log2e), |r| <= 0.35
+    const float e = __int_as_float(__float_as_int(m) + (__float_as_int(t) << 23));  // * 2^n
+    const float d = 1.0f + e;
+    float q;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q) : "f"(d));
+    const float err = fmaf(-d, q, 1.0f);
+    return fmaf(q, err, q);
   } else {
     return 1.0f / (1.0f + expf(-v));
   }

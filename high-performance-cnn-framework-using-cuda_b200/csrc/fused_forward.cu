@@ -32,7 +32,7 @@ struct FwSmem {
   unsigned long long full[kFwStages];
 };
 
-template <bool FAST, int MINB>
+template <int FAST, int MINB>
 __global__ void __launch_bounds__(kFwThreads, MINB)
 k_fused_forward(const float* __restrict__ images, long n, const float* __restrict__ params,
                 float* __restrict__ out, int* __restrict__ argmax, int* __restrict__ status) {
@@ -182,7 +182,7 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
   }
 }
 
-template <bool FAST, int MINB>
+template <int FAST, int MINB>
 static int launch_variant(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
   const long n_tiles = (n + kFwImgs - 1) / kFwImgs;
@@ -198,15 +198,20 @@ static int launch_variant(cnn_net* net, const float* d_images, long n, float* d_
   return CNN_OK;
 }
 
-// fw_variant: 0 = two blocks per SM (register-capped), 1 = one block per SM (no cap).
+// fw_variant: 2 (default) = packed-FMA kernel of fused_forward_x2.cu; the scalar kernel of this file
+// is kept for comparison: 0 = two blocks per SM (register-capped), 1 = one block per SM (no cap);
 static int launch_forward(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
+  if (net->fw_variant >= 2) return launch_forward_x2(net, d_images, n, d_out, d_argmax, stream);
+  const int fl = net->fast_sigmoid;
   if (net->fw_variant == 1) {
-    return net->fast_sigmoid ? launch_variant<true, 1>(net, d_images, n, d_out, d_argmax, stream)
-                             : launch_variant<false, 1>(net, d_images, n, d_out, d_argmax, stream);
+    return fl == 1 ? launch_variant<1, 1>(net, d_images, n, d_out, d_argmax, stream)
+         : fl == 2 ? launch_variant<2, 1>(net, d_images, n, d_out, d_argmax, stream)
+                   : launch_variant<0, 1>(net, d_images, n, d_out, d_argmax, stream);
   }
-  return net->fast_sigmoid ? launch_variant<true, 2>(net, d_images, n, d_out, d_argmax, stream)
-                           : launch_variant<false, 2>(net, d_images, n, d_out, d_argmax, stream);
+  return fl == 1 ? launch_variant<1, 2>(net, d_images, n, d_out, d_argmax, stream)
+       : fl == 2 ? launch_variant<2, 2>(net, d_images, n, d_out, d_argmax, stream)
+                 : launch_variant<0, 2>(net, d_images, n, d_out, d_argmax, stream);
 }
 
 int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,

@@ -62,7 +62,7 @@ struct FwdRegs {
   float wfv[kOut]; // this thread's column of the FC weights
 };
 
-template <bool FAST>
+template <int FAST>
 __device__ __forceinline__ void thread_forward(const TrSmem& sm, const float* img, int f, int p, int q,
                                                int s, bool live, FwdRegs& r, float (&pk)[kOut]) {
   if (live) {
@@ -164,7 +164,7 @@ __device__ __forceinline__ void thread_backward(const TrSmem& sm, const FwdRegs&
 constexpr int kRowStride = kNParamsPadded + 8;
 constexpr int kRowErr = kNParams + 1;  // 2344
 
-template <bool FAST>
+template <int FAST>
 __global__ void __launch_bounds__(kTrThreads, 1)
 k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ labels, long n,
                 const float* __restrict__ params, float* __restrict__ rows, int* __restrict__ status) {
@@ -334,7 +334,7 @@ __global__ void k_apply_update(float* __restrict__ params, const float* __restri
 // ----------------------------------------------------------------------------------------------
 // Per-sample SGD, one persistent block.
 // ----------------------------------------------------------------------------------------------
-template <bool FAST>
+template <int FAST>
 __global__ void __launch_bounds__(kTrThreads, 1)
 k_train_persample(const float* __restrict__ images, const unsigned* __restrict__ labels, long n,
                   int epochs, float dt, float threshold, float* __restrict__ params,
@@ -481,15 +481,16 @@ static int launch_grad_partials(cnn_net* net, const float* d_images, const unsig
                                 int grid, cudaStream_t st) {
   const size_t smem = sizeof(TrSmem);
   int rc;
-  if (net->fast_sigmoid) {
-    if ((rc = set_smem_attr(k_grad_partials<true>, smem)) != CNN_OK) return rc;
-    k_grad_partials<true><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params,
-                                                          net->d_partials, net->d_status);
-  } else {
-    if ((rc = set_smem_attr(k_grad_partials<false>, smem)) != CNN_OK) return rc;
-    k_grad_partials<false><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params,
-                                                           net->d_partials, net->d_status);
-  }
+#define CNN_LAUNCH_GRAD(FL)                                                                        \
+  do {                                                                                             \
+    if ((rc = set_smem_attr(k_grad_partials<FL>, smem)) != CNN_OK) return rc;                      \
+    k_grad_partials<FL><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params,      \
+                                                        net->d_partials, net->d_status);           \
+  } while (0)
+  if (net->fast_sigmoid == 1) CNN_LAUNCH_GRAD(1);
+  else if (net->fast_sigmoid == 2) CNN_LAUNCH_GRAD(2);
+  else CNN_LAUNCH_GRAD(0);
+#undef CNN_LAUNCH_GRAD
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch");
   return CNN_OK;
@@ -531,6 +532,7 @@ int cnn_grad_batch(cnn_net* net, const float* d_images, const unsigned int* d_la
 
 int cnn_apply_update(cnn_net* net, const float* d_grad, float scale, void* stream) {
   CNN_REQUIRE(net && d_grad, "cnn_apply_update: NULL argument");
+  ++net->params_version;
   k_apply_update<<<(kNParams + 255) / 256, 256, 0, as_stream(stream)>>>(net->d_params, d_grad, scale);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_apply_update launch");
@@ -546,6 +548,7 @@ int cnn_train_minibatch(cnn_net* net, const float* d_images, const unsigned int*
   CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
               "cnn_train_minibatch: image batch must start on a 16-byte boundary");
   cudaStream_t st = as_stream(stream);
+  ++net->params_version;
   int rc = ensure_train_scratch(net, sm_count());
   if (rc != CNN_OK) return rc;
   if (d_mean_err) CNN_CUDA(cudaMemsetAsync(d_mean_err, 0, sizeof(float) * (size_t)epochs, st));
@@ -576,6 +579,7 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
               "cnn_train_sgd_persample: image batch must start on a 16-byte boundary");
   cudaStream_t st = as_stream(stream);
+  ++net->params_version;
   int rc = ensure_train_scratch(net, sm_count());
   if (rc != CNN_OK) return rc;
   // Scratch reuse: d_grad holds the per-epoch means (epochs <= kNParamsPadded) and the epoch count.
@@ -583,15 +587,16 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   float* d_mean = net->d_grad;
   int* d_ran = reinterpret_cast<int*>(net->d_grad + kNParamsPadded);
   const size_t smem = sizeof(TrSmem);
-  if (net->fast_sigmoid) {
-    if ((rc = set_smem_attr(k_train_persample<true>, smem)) != CNN_OK) return rc;
-    k_train_persample<true><<<1, kTrThreads, smem, st>>>(d_images, d_labels, n, epochs, dt, threshold,
-                                                        net->d_params, d_mean, d_ran, net->d_status);
-  } else {
-    if ((rc = set_smem_attr(k_train_persample<false>, smem)) != CNN_OK) return rc;
-    k_train_persample<false><<<1, kTrThreads, smem, st>>>(d_images, d_labels, n, epochs, dt, threshold,
-                                                         net->d_params, d_mean, d_ran, net->d_status);
-  }
+#define CNN_LAUNCH_PS(FL)                                                                          \
+  do {                                                                                             \
+    if ((rc = set_smem_attr(k_train_persample<FL>, smem)) != CNN_OK) return rc;                    \
+    k_train_persample<FL><<<1, kTrThreads, smem, st>>>(d_images, d_labels, n, epochs, dt, threshold, \
+                                                       net->d_params, d_mean, d_ran, net->d_status); \
+  } while (0)
+  if (net->fast_sigmoid == 1) CNN_LAUNCH_PS(1);
+  else if (net->fast_sigmoid == 2) CNN_LAUNCH_PS(2);
+  else CNN_LAUNCH_PS(0);
+#undef CNN_LAUNCH_PS
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_train_persample launch");
   CNN_CUDA(cudaStreamSynchronize(st));

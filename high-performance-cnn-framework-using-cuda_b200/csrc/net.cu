@@ -49,6 +49,9 @@ int cnn_net_create(unsigned int seed, cnn_net** out) {
   *out = nullptr;
   cnn_net* net = new (std::nothrow) cnn_net();
   CNN_REQUIRE(net != nullptr, "cnn_net_create: out of host memory");
+  static int next_id = 0;
+  net->id = ++next_id;
+  net->const_slot = net->id % 8;
   cudaError_t e = cudaGetDevice(&net->device);
   if (e == cudaSuccess) e = cudaMalloc(&net->d_params, sizeof(float) * kNParamsPadded);
   if (e == cudaSuccess) e = cudaMalloc(&net->d_status, sizeof(int));
@@ -101,6 +104,7 @@ int cnn_net_destroy(cnn_net* net) {
 int cnn_net_set_params(cnn_net* net, const float* h_params) {
   CNN_REQUIRE(net && h_params, "cnn_net_set_params: NULL argument");
   CNN_CUDA(cudaMemcpy(net->d_params, h_params, sizeof(float) * kNParams, cudaMemcpyHostToDevice));
+  ++net->params_version;
   return CNN_OK;
 }
 
@@ -113,12 +117,13 @@ int cnn_net_get_params(cnn_net* net, float* h_params) {
 int cnn_net_params_device(cnn_net* net, float** d_params) {
   CNN_REQUIRE(net && d_params, "cnn_net_params_device: NULL argument");
   *d_params = net->d_params;
+  ++net->params_version;  // the caller may write through the pointer
   return CNN_OK;
 }
 
 int cnn_net_set_fast_sigmoid(cnn_net* net, int enable) {
   CNN_REQUIRE(net, "cnn_net_set_fast_sigmoid: NULL net");
-  net->fast_sigmoid = enable ? 1 : 0;
+  net->fast_sigmoid = (enable == 2) ? 2 : (enable ? 1 : 0);
   return CNN_OK;
 }
 
@@ -129,7 +134,7 @@ int cnn_net_set_option(cnn_net* net, const char* key, int value) {
     return CNN_OK;
   }
   if (std::strcmp(key, "fast_sigmoid") == 0) {
-    net->fast_sigmoid = value ? 1 : 0;
+    net->fast_sigmoid = (value == 2) ? 2 : (value ? 1 : 0);
     return CNN_OK;
   }
   set_error("cnn_net_set_option: unknown option '%s'", key);

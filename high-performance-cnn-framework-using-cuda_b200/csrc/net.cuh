@@ -5,10 +5,13 @@
 
 struct cnn_net {
   int device = 0;
+  int id = 0;                      // process-unique, > 0
+  int const_slot = 0;              // constant-bank slot of this net (scalar forward variant)
+  long params_version = 1;         // bumped whenever the arena may have changed
   float* d_params = nullptr;       // kNParamsPadded floats
   int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out
-  int fast_sigmoid = 0;
-  int fw_variant = 0;              // forward kernel variant (tuning knob, see cnn_net_set_option)
+  int fast_sigmoid = 0;            // sigmoid flavour 0 / 1 / 2, see sigmoidf in cnn_common.cuh
+  int fw_variant = 0;              // forward kernel: 0 = scalar kernel, two blocks per SM (default); 1, 2, 3 = experiments
 
   // Training scratch (allocated on first use): per-block partial gradients and the reduced vector.
   float* d_partials = nullptr;     // [partial_rows][kNParamsPadded]
@@ -79,5 +82,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 }
 
 int ensure_train_scratch(cnn_net* net, int rows);
+int launch_forward_x2(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+                      cudaStream_t stream);
 
 }  // namespace cnn

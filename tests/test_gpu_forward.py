@@ -26,8 +26,8 @@ def clear_margin(out, tol=1e-5):
     return (top2[:, -1] - top2[:, -2]) > tol * top2[:, -1]
 
 
-@pytest.mark.parametrize("fast", [False, True])
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("fast", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("n", [1, 7, 8, 9, 100, 2368 + 5, 4099])
 def test_forward_matches_oracle(cuda, pkg, ob, params0, n, fast, variant):
     images, _ = pkg.synth.synth_images(21, n)

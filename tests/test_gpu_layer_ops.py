@@ -162,7 +162,9 @@ def test_operators_are_deterministic(cuda, pkg, params0, data64):
     assert np.array_equal(runs[0], runs[1])
 
 
-@pytest.mark.parametrize("shape", [(64, 64), (1, 32), (148, 256), (3, 7), (10, 1)])
+# The reference kernels compute N * thread_index in int, so with N = 86,400 they are only valid for
+# launches of fewer than 24,855 threads; (96, 256) is the largest shape tried.
+@pytest.mark.parametrize("shape", [(64, 64), (1, 32), (96, 256), (3, 7), (10, 1)])
 def test_against_reference_kernels(cuda, pkg, ob, params0, data64, shape):
     """Same inputs through the reference's own CUDA kernels (unmodified layer.cu)."""
     if not ob.reference_available():

@@ -11,6 +11,22 @@ BLOCKS = {"Wc": (0, 150), "bc": (150, 156), "Ws": (156, 172), "bs": (172, 173), 
           "bf": (2333, 2343)}
 
 
+# In-place adds per step into one parameter: the reference (and the oracle, which follows it) adds
+# every bias term straight into the bias, 576 times for a conv bias and 216 times for the subsample bias.
+SEQUENTIAL_ADDS = {"Wc": 1, "bc": 576, "Ws": 1, "bs": 216, "Wf": 1, "bf": 1}
+
+
+def increments_agree(p, p_other, p0, lo, hi, name, rtol=1e-4):
+    """Compare parameter increments of one block.  An increment is only known to the rounding of the
+    parameter it was added to (half an ulp of |p| per add, a random walk over the adds), so the bar
+    is rtol of the block's largest increment plus 2*sqrt(adds) ulps of the block's largest parameter."""
+    inc_a = p[lo:hi].astype(np.float64) - p0[lo:hi]
+    inc_b = p_other[lo:hi].astype(np.float64) - p0[lo:hi]
+    ulp = float(np.spacing(np.float32(np.max(np.abs(p0[lo:hi])))))
+    slack = 2 * ulp * np.sqrt(SEQUENTIAL_ADDS[name])
+    return np.max(np.abs(inc_a - inc_b)) <= rtol * np.max(np.abs(inc_b)) + slack
+
+
 def to_dev(torch, images, labels):
     d_img = torch.from_numpy(np.ascontiguousarray(images)).cuda()
     d_lab = torch.from_numpy(np.ascontiguousarray(labels).astype(np.int32)).cuda()
@@ -26,7 +42,7 @@ def gpu_grad(torch, net, images, labels):
     return d_g.cpu().numpy()
 
 
-@pytest.mark.parametrize("fast", [False, True])
+@pytest.mark.parametrize("fast", [0, 1, 2])
 @pytest.mark.parametrize("n", [1, 2, 147, 148, 149, 256, 1000])
 def test_grad_batch_matches_oracle(cuda, pkg, ob, params0, n, fast):
     images, labels = pkg.synth.synth_images(31, n)
@@ -80,7 +96,7 @@ def test_single_sgd_step_matches_oracle_and_reference(cuda, pkg, ob, params0, da
         assert ran == 1
         assert scaled_err(p, p_or) < 1e-5
         for name, (lo, hi) in BLOCKS.items():
-            assert scaled_err(p[lo:hi] - params0[lo:hi], p_or[lo:hi] - params0[lo:hi]) < 1e-4, name
+            assert increments_agree(p, p_or, params0, lo, hi, name), name
         assert abs(float(mean_err[0]) - err_or) < 1e-5
         if ref is not None:
             ref.set_params(params0)
@@ -88,13 +104,13 @@ def test_single_sgd_step_matches_oracle_and_reference(cuda, pkg, ob, params0, da
             p_ref = ref.get_params()
             assert scaled_err(p, p_ref) < 1e-5
             for name, (lo, hi) in BLOCKS.items():
-                assert scaled_err(p[lo:hi] - params0[lo:hi], p_ref[lo:hi] - params0[lo:hi]) < 1e-4, name
+                assert increments_agree(p, p_ref, params0, lo, hi, name), name
             assert abs(float(mean_err[0]) - err_ref) < 1e-5
     if ref is not None:
         ref.close()
 
 
-@pytest.mark.parametrize("fast", [False, True])
+@pytest.mark.parametrize("fast", [0, 1, 2])
 def test_persample_trajectory_matches_oracle(cuda, pkg, ob, params0, fast):
     """2,000 sequential SGD steps (two epochs of 1,000).  Rounding differences compound along the
     chain, so the bar on parameters is 1e-3 of the largest parameter here, with 1e-5 kept for the
