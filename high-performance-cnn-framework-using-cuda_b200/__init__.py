@@ -102,6 +102,7 @@ _PROTOTYPES = {
     "cnn_copy_to_host": (C.c_int, [_P, _P, C.c_size_t]),
     "cnn_copy_to_device": (C.c_int, [_P, _P, C.c_size_t]),
     "cnn_grad_batch": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
+    "cnn_grad_batch_noalloc": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
     "cnn_apply_update": (C.c_int, [_P, _P, C.c_float, _P]),
     "cnn_train_minibatch": (C.c_int, [_P, _P, _P, C.c_long, C.c_int, C.c_int, C.c_float, _P, _P]),
     "cnn_train_sgd_persample": (C.c_int, [_P, _P, _P, C.c_long, C.c_int, C.c_float, C.c_float, _P, C.POINTER(C.c_int), _P]),
@@ -368,6 +369,15 @@ class Net:
             self.close()
         except Exception:
             pass
+
+
+def grad_batch_noalloc(d_params, d_images, d_labels, n: int, d_grad, stream=None) -> None:
+    """Summed gradient of n images at the parameters in ``d_params`` (2343 device floats) into
+    ``d_grad`` (2368 device floats), for callers that may not allocate device memory: no ``Net`` is
+    involved and the call allocates nothing (its scratch is a fixed array inside the library).  At
+    most 65,536 images per call; calls that can overlap on the GPU share that array and race."""
+    _check(load_library().cnn_grad_batch_noalloc(_ptr(d_params), _ptr(d_images), _ptr(d_labels), int(n),
+                                                 _ptr(d_grad), _stream(stream)))
 
 
 def synth_images_device(seed: int, first_index: int, n: int, d_images, d_labels=None, stream=None) -> None:

@@ -616,6 +616,76 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   return CNN_OK;
 }
 
+// ----------------------------------------------------------------------------------------------
+// Gradient of a batch without any allocation.
+//
+// Some callers may not allocate device memory at the point where they need a gradient: code that
+// runs inside a memory-budgeted service whose pools are carved up at start-up, plug-ins that are
+// handed device buffers by a host application and are forbidden to call cudaMalloc themselves,
+// and real-time loops where an allocation (a device-wide synchronisation) is not acceptable.
+// cnn_grad_batch needs a cnn_net, and creating one allocates; this entry point takes raw device
+// pointers instead and keeps the partial-gradient rows of k_grad_partials in a fixed array that is
+// part of the library image.
+// ----------------------------------------------------------------------------------------------
+namespace cnn {
+constexpr int kNoAllocMaxRows = 160;          // one row per block, at most this many blocks
+constexpr long kNoAllocMaxImages = 65536;     // largest batch the entry point accepts
+// rows | status word (+ padding to keep the array a multiple of 256 bytes)
+constexpr size_t kNoAllocFloats = (size_t)kNoAllocMaxRows * kRowStride + 64;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+}  // namespace cnn
+
+int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const unsigned int* d_labels,
+                           long n, float* d_grad, void* stream) {
+  CNN_REQUIRE(d_params && d_grad, "cnn_grad_batch_noalloc: NULL params or gradient buffer");
+  CNN_REQUIRE(n >= 0, "cnn_grad_batch_noalloc: negative image count");
+  if (n > kNoAllocMaxImages) {
+    set_error("cnn_grad_batch_noalloc: %ld images exceed the fixed-scratch limit of %ld per call; "
+              "split the batch (gradients add) or use cnn_grad_batch", n, kNoAllocMaxImages);
+    return CNN_ERR_INVALID;
+  }
+  cudaStream_t st = as_stream(stream);
+  if (n == 0) {
+    CNN_CUDA(cudaMemsetAsync(d_grad, 0, sizeof(float) * kNParamsPadded, st));
+    return CNN_OK;
+  }
+  CNN_REQUIRE(d_images && d_labels, "cnn_grad_batch_noalloc: NULL images or labels");
+  CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
+              "cnn_grad_batch_noalloc: image batch must start on a 16-byte boundary");
+
+  // Set-up, once per device, with that device current: in host code the array's name is only a
+  // handle, its device address has to be asked for.
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  CNN_CUDA(cudaGetDevice(&dev));
+  CNN_REQUIRE(dev >= 0 && dev < 64, "cnn_grad_batch_noalloc: device ordinal out of range");
+  if (scratch_of_device[dev] == nullptr) {
+    float* ptr = nullptr;
+    CNN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch));
+    CNN_REQUIRE(ptr != nullptr, "cnn_grad_batch_noalloc: no device address for the scratch array");
+    CNN_CUDA(cudaFuncSetAttribute(k_grad_partials<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)sizeof(TrSmem)));
+    scratch_of_device[dev] = ptr;
+  }
+  float* rows = scratch_of_device[dev];
+  int* status = reinterpret_cast<int*>(rows + (size_t)kNoAllocMaxRows * kRowStride);
+
+  long grid_l = sm_count();
+  if (grid_l > kNoAllocMaxRows) grid_l = kNoAllocMaxRows;
+  if (grid_l > n) grid_l = n;
+  const int grid = (int)grid_l;
+  // The array keeps what the previous call left: the status word must start at zero (every row that
+  // is read below is rewritten in full by its block, padding included).
+  CNN_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  k_grad_partials<0><<<grid, kTrThreads, sizeof(TrSmem), st>>>(d_images, d_labels, n, d_params, rows, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch (no-alloc)");
+  k_reduce_rows<<<(kNParamsPadded + 31) / 32, 128, 0, st>>>(rows, grid, d_grad, nullptr, 0.f, nullptr, 0.f);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "k_reduce_rows launch (no-alloc)");
+  return CNN_OK;
+}
+
 int cnn_copy_to_host(void* h_dst, const void* d_src, size_t bytes) {
   CNN_REQUIRE(h_dst && d_src, "cnn_copy_to_host: NULL argument");
   CNN_CUDA(cudaMemcpy(h_dst, d_src, bytes, cudaMemcpyDeviceToHost));

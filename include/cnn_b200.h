@@ -188,6 +188,23 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
                             int epochs, float dt, float threshold, float* h_mean_err, int* h_epochs_run,
                             void* stream);
 
+/* No counterpart in the reference.  The same computation as cnn_grad_batch for callers that must
+ * not allocate device memory: no cnn_net is needed (creating one allocates), only raw device
+ * pointers -- d_params (2343 floats, arena order), the images and labels, and d_grad (2368 floats,
+ * same layout as cnn_grad_batch).  Nothing in this call allocates or frees, on the device or through
+ * any library: the per-block partial rows live in a 1.5 MB array inside the library image
+ * (160 rows; every GPU that loads the library holds that memory until the process exits).
+ *   - at most 65,536 images per call; larger batches are rejected with CNN_ERR_INVALID (split them:
+ *     gradients of sub-batches add);
+ *   - the first call on each device looks up the array's device address and raises the kernel's
+ *     shared-memory limit; make that first call outside any stream capture;
+ *   - all calls on one device share the one array (it still holds the previous call's rows), so two
+ *     calls whose kernels can overlap on the GPU -- different streams, or different host threads --
+ *     race; serialise them on one stream or with events;
+ *   - the reference sigmoid (flavour 0) is used. */
+int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const unsigned int* d_labels,
+                           long n, float* d_grad, void* stream);
+
 /* Blocking copies between host and device memory (for bindings without a CUDA runtime of their own). */
 int cnn_copy_to_host(void* h_dst, const void* d_src, size_t bytes);
 int cnn_copy_to_device(void* d_dst, const void* h_src, size_t bytes);
