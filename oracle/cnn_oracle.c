@@ -13,10 +13,11 @@
  * with -ffp-contract=off; the two places where nvcc does contract (apply_grad, bp_bias_f:
  * "x += dt * g") call fma() explicitly.
  *
- * Parity status: "parity unpinned" by any golden vector of the reference (it ships no tests, no
- * fixtures, no recorded output).  The pin is the reference's own kernels, compiled unmodified into
- * oracle/_ref/libref_cnn.so (see ref_harness.cu / build_oracle.py) and run next to this
- * restatement on a GPU by the -m gpu tests.
+ * Parity status: pinned.  The reference ships no tests, fixtures or recorded outputs, so the pin is
+ * the reference's own kernels: compiled unmodified into oracle/_ref/libref_cnn.so (ref_harness.cu,
+ * build_oracle.py) they are run next to this restatement by the -m gpu tests, and their outputs on
+ * seeded inputs, recorded on a B200 (tests/golden/make_golden.py), are committed under tests/golden/
+ * and checked against this file by the CPU tests.
  *
  * The same source is compiled twice: REAL=float (symbols *_f32, the oracle proper) and REAL=double
  * (symbols *_f64, used to bound fp32 rounding).
