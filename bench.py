@@ -335,6 +335,17 @@ def run_ours(args):
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_value = world * BATCH * e2e_steps / e2e_s
     barrier()
+    # the same call on uint8 pixels (the IDX storage the reference's loader reads): a quarter of the bytes
+    h_pix = torch.from_numpy(pkg.synth.synth_pixels_u8(1, 4096)).repeat(BATCH // 4096, 1, 1).contiguous().pin_memory()
+    for _ in range(2):
+        net.forward_u8_host(h_pix, BATCH, h_out, h_arg)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        net.forward_u8_host(h_pix, BATCH, h_out, h_arg)
+    torch.cuda.synchronize()
+    e2e_u8_value = world * BATCH * e2e_steps / max_over_ranks(time.perf_counter() - t0)
+    barrier()
 
     # ---- extra: training legs -------------------------------------------------------------------
     train = {}
@@ -431,6 +442,9 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": BATCH * 3136,
                 "d2h_bytes_per_step": BATCH * 44, "steps": e2e_steps,
                 "api": "cnn_forward_batched_host (pinned host buffers, 8,192-image chunks on two streams)"},
+        "e2e_u8": {"value": e2e_u8_value, "unit": "images/s", "h2d_bytes_per_step": BATCH * 784,
+                   "d2h_bytes_per_step": BATCH * 44, "api": "cnn_forward_batched_u8_host (uint8 pixels, "
+                   "pixel/255.0 applied in the kernel; bit-identical results)"},
         "gpu_launches": args.steps * world,
         "clocks": clocks,
     }

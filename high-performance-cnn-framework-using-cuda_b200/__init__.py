@@ -98,6 +98,8 @@ _PROTOTYPES = {
     "cnn_net_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "cnn_forward_batched": (C.c_int, [_P, _P, C.c_long, _P, _P, _P]),
     "cnn_forward_batched_host": (C.c_int, [_P, _P, C.c_long, _P, _P]),
+    "cnn_forward_batched_u8": (C.c_int, [_P, _P, C.c_long, _P, _P, _P]),
+    "cnn_forward_batched_u8_host": (C.c_int, [_P, _P, C.c_long, _P, _P]),
     "cnn_synth_images": (C.c_int, [C.c_ulonglong, C.c_long, C.c_long, _P, _P, _P]),
     "cnn_copy_to_host": (C.c_int, [_P, _P, C.c_size_t]),
     "cnn_copy_to_device": (C.c_int, [_P, _P, C.c_size_t]),
@@ -331,6 +333,16 @@ class Net:
         """Same through host buffers (pinned memory gives asynchronous copies)."""
         _check(load_library().cnn_forward_batched_host(self._h, _ptr(h_images), int(n), _ptr(h_out),
                                                        _ptr(h_argmax)))
+
+    def forward_u8(self, d_pixels, n: int, d_out=None, d_argmax=None, stream=None) -> None:
+        """Fused forward on uint8 pixels [n,28,28] (IDX storage); same results as ``forward`` on
+        ``pixels / 255.0``."""
+        _check(load_library().cnn_forward_batched_u8(self._h, _ptr(d_pixels), int(n), _ptr(d_out),
+                                                     _ptr(d_argmax), _stream(stream)))
+
+    def forward_u8_host(self, h_pixels, n: int, h_out=None, h_argmax=None) -> None:
+        _check(load_library().cnn_forward_batched_u8_host(self._h, _ptr(h_pixels), int(n), _ptr(h_out),
+                                                          _ptr(h_argmax)))
 
     # -- training -----------------------------------------------------------------------------
     def grad_batch(self, d_images, d_labels, n: int, d_grad, stream=None) -> None:

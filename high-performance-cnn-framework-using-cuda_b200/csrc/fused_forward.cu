@@ -29,10 +29,14 @@ struct FwSmem {
   float wf[kOut][kS];                       // [k][f*36 + window]
   float bf[12];
   float part[kFwImgs][kOut][kPartStride];
+  float lut[256];                           // uint8 pixel -> float(pixel / 255.0), uint8 input only
   unsigned long long full[kFwStages];
 };
 
-template <int FAST, int MINB>
+// U8 = false: images are fp32 [n][28][28].  U8 = true: `images` points at uint8 pixels [n][28][28]
+// (the storage of the IDX files the reference reads) and the kernel applies the reference's ingest,
+// float(pixel / 255.0) (mnist.h:145 then main.cu:57-65), through a 256-entry table.
+template <int FAST, int MINB, bool U8>
 __global__ void __launch_bounds__(kFwThreads, MINB)
 k_fused_forward(const float* __restrict__ images, long n, const float* __restrict__ params,
                 float* __restrict__ out, int* __restrict__ argmax, int* __restrict__ status) {
@@ -51,6 +55,7 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
   if (tid == 0) sm.bs[0] = params[kOffBs];
   for (int i = tid; i < kOut * kS; i += kFwThreads) sm.wf[i / kS][i % kS] = params[kOffWf + i];
   if (tid < kOut) sm.bf[tid] = params[kOffBf + tid];
+  if (U8 && tid < 256) sm.lut[tid] = (float)((double)tid / 255.0);
 
   if (tid == 0) {
     for (int s = 0; s < kFwStages; ++s) mbar_init(&sm.full[s], 1);
@@ -62,9 +67,11 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
     const long first = tile * kFwImgs;
     const long left = n - first;
     const unsigned cnt = (unsigned)(left < kFwImgs ? left : kFwImgs);
-    const unsigned bytes = cnt * (unsigned)(kImg * sizeof(float));
+    constexpr unsigned kPixelBytes = U8 ? 1u : (unsigned)sizeof(float);
+    const unsigned bytes = cnt * (unsigned)kImg * kPixelBytes;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(images) + (size_t)first * kImg * kPixelBytes;
     mbar_expect_tx(&sm.full[stage], bytes);
-    bulk_g2s(&sm.img[stage][0][0], images + first * kImg, bytes, &sm.full[stage]);
+    bulk_g2s(&sm.img[stage][0][0], src, bytes, &sm.full[stage]);
   };
 
   if (tid == 0) {
@@ -91,7 +98,20 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
 
     // 8x8 input patch of this thread's window: rows 4p..4p+7, columns 4q..4q+7.
     float patch[8][8];
-    if (live) {
+    if (live && U8) {
+      const unsigned char* bytes0 = reinterpret_cast<const unsigned char*>(&sm.img[stage][0][0]);
+      const unsigned char* base = bytes0 + img * kImg + (4 * p) * kH + 4 * q;  // 4-byte aligned
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const unsigned lo = *reinterpret_cast<const unsigned*>(base + r * kH);
+        const unsigned hi = *reinterpret_cast<const unsigned*>(base + r * kH + 4);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          patch[r][c] = sm.lut[(lo >> (8 * c)) & 0xFFu];
+          patch[r][4 + c] = sm.lut[(hi >> (8 * c)) & 0xFFu];
+        }
+      }
+    } else if (live) {
       const float* base = &sm.img[stage][img][(4 * p) * kH + 4 * q];
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
@@ -182,41 +202,49 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
   }
 }
 
-template <int FAST, int MINB>
-static int launch_variant(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+template <int FAST, int MINB, bool U8>
+static int launch_variant(cnn_net* net, const void* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
   const long n_tiles = (n + kFwImgs - 1) / kFwImgs;
   const long max_blocks = (long)MINB * sm_count();
   const int grid = (int)(n_tiles < max_blocks ? n_tiles : max_blocks);
   const size_t smem = sizeof(FwSmem);
-  CNN_CUDA(cudaFuncSetAttribute(k_fused_forward<FAST, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  CNN_CUDA(cudaFuncSetAttribute(k_fused_forward<FAST, MINB, U8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)smem));
-  k_fused_forward<FAST, MINB><<<grid, kFwThreads, smem, stream>>>(d_images, n, net->d_params, d_out,
-                                                                 d_argmax, net->d_status);
+  k_fused_forward<FAST, MINB, U8><<<grid, kFwThreads, smem, stream>>>(
+      static_cast<const float*>(d_images), n, net->d_params, d_out, d_argmax, net->d_status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_fused_forward launch");
   return CNN_OK;
 }
 
-// fw_variant: 2 (default) = packed-FMA kernel of fused_forward_x2.cu; the scalar kernel of this file
-// is kept for comparison: 0 = two blocks per SM (register-capped), 1 = one block per SM (no cap);
+// fw_variant: 0 (default) = the scalar kernel of this file, two blocks per SM (register-capped);
+// 1 = the same with one block per SM (no cap); 2, 3 = the experiments of fused_forward_x2.cu.
 static int launch_forward(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
   if (net->fw_variant >= 2) return launch_forward_x2(net, d_images, n, d_out, d_argmax, stream);
   const int fl = net->fast_sigmoid;
   if (net->fw_variant == 1) {
-    return fl == 1 ? launch_variant<1, 1>(net, d_images, n, d_out, d_argmax, stream)
-         : fl == 2 ? launch_variant<2, 1>(net, d_images, n, d_out, d_argmax, stream)
-                   : launch_variant<0, 1>(net, d_images, n, d_out, d_argmax, stream);
+    return fl == 1 ? launch_variant<1, 1, false>(net, d_images, n, d_out, d_argmax, stream)
+         : fl == 2 ? launch_variant<2, 1, false>(net, d_images, n, d_out, d_argmax, stream)
+                   : launch_variant<0, 1, false>(net, d_images, n, d_out, d_argmax, stream);
   }
-  return fl == 1 ? launch_variant<1, 2>(net, d_images, n, d_out, d_argmax, stream)
-       : fl == 2 ? launch_variant<2, 2>(net, d_images, n, d_out, d_argmax, stream)
-                 : launch_variant<0, 2>(net, d_images, n, d_out, d_argmax, stream);
+  return fl == 1 ? launch_variant<1, 2, false>(net, d_images, n, d_out, d_argmax, stream)
+       : fl == 2 ? launch_variant<2, 2, false>(net, d_images, n, d_out, d_argmax, stream)
+                 : launch_variant<0, 2, false>(net, d_images, n, d_out, d_argmax, stream);
 }
 
 int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                    cudaStream_t stream) {
   return launch_forward(net, d_images, n, d_out, d_argmax, stream);
+}
+
+int forward_device_u8(cnn_net* net, const unsigned char* d_pixels, long n, float* d_out, int* d_argmax,
+                      cudaStream_t stream) {
+  const int fl = net->fast_sigmoid;
+  return fl == 1 ? launch_variant<1, 2, true>(net, d_pixels, n, d_out, d_argmax, stream)
+       : fl == 2 ? launch_variant<2, 2, true>(net, d_pixels, n, d_out, d_argmax, stream)
+                 : launch_variant<0, 2, true>(net, d_pixels, n, d_out, d_argmax, stream);
 }
 
 }  // namespace cnn
@@ -230,4 +258,15 @@ extern "C" int cnn_forward_batched(cnn_net* net, const float* d_images, long n, 
   CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
               "cnn_forward_batched: image batch must start on a 16-byte boundary");
   return cnn::forward_device(net, d_images, n, d_out, d_argmax, cnn::as_stream(stream));
+}
+
+extern "C" int cnn_forward_batched_u8(cnn_net* net, const unsigned char* d_pixels, long n, float* d_out,
+                                      int* d_argmax, void* stream) {
+  CNN_REQUIRE(net != nullptr, "cnn_forward_batched_u8: NULL net");
+  CNN_REQUIRE(n >= 0, "cnn_forward_batched_u8: negative image count");
+  if (n == 0) return CNN_OK;
+  CNN_REQUIRE(d_pixels != nullptr, "cnn_forward_batched_u8: NULL pixels");
+  CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_pixels) & 15u) == 0,
+              "cnn_forward_batched_u8: pixel batch must start on a 16-byte boundary");
+  return cnn::forward_device_u8(net, d_pixels, n, d_out, d_argmax, cnn::as_stream(stream));
 }

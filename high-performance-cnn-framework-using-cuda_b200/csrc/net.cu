@@ -9,6 +9,8 @@
 namespace cnn {
 int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                    cudaStream_t stream);
+int forward_device_u8(cnn_net* net, const unsigned char* d_pixels, long n, float* d_out, int* d_argmax,
+                      cudaStream_t stream);
 
 int ensure_train_scratch(cnn_net* net, int rows) {
   if (!net->d_grad) CNN_CUDA(cudaMalloc(&net->d_grad, sizeof(float) * (kNParamsPadded + 8)));
@@ -154,12 +156,15 @@ int cnn_net_status(cnn_net* net, int* status) {
   return CNN_OK;
 }
 
-int cnn_forward_batched_host(cnn_net* net, const float* h_images, long n, float* h_out,
+}  // extern "C"
+
+static int forward_host_impl(cnn_net* net, const void* h_images, bool u8, long n, float* h_out,
                              int* h_argmax) {
   CNN_REQUIRE(net != nullptr, "cnn_forward_batched_host: NULL net");
   CNN_REQUIRE(n >= 0, "cnn_forward_batched_host: negative image count");
   if (n == 0) return CNN_OK;
   CNN_REQUIRE(h_images != nullptr, "cnn_forward_batched_host: NULL images");
+  const size_t image_bytes = u8 ? (size_t)kImg : sizeof(float) * kImg;
   int rc = ensure_stage(net);
   if (rc != CNN_OK) return rc;
   // Two staging slots, one stream each: within a slot the copy-in, the kernel and the copy-out
@@ -170,10 +175,13 @@ int cnn_forward_batched_host(cnn_net* net, const float* h_images, long n, float*
   while (done < n) {
     const long cnt = (n - done) < net->stage_images ? (n - done) : net->stage_images;
     cudaStream_t st = net->copy_stream[slot];
-    CNN_CUDA(cudaMemcpyAsync(net->d_stage_img[slot], h_images + done * kImg,
-                             sizeof(float) * (size_t)cnt * kImg, cudaMemcpyHostToDevice, st));
-    rc = forward_device(net, net->d_stage_img[slot], cnt, net->d_stage_out[slot],
-                        net->d_stage_arg[slot], st);
+    CNN_CUDA(cudaMemcpyAsync(net->d_stage_img[slot],
+                             static_cast<const unsigned char*>(h_images) + (size_t)done * image_bytes,
+                             (size_t)cnt * image_bytes, cudaMemcpyHostToDevice, st));
+    rc = u8 ? forward_device_u8(net, reinterpret_cast<const unsigned char*>(net->d_stage_img[slot]), cnt,
+                                net->d_stage_out[slot], net->d_stage_arg[slot], st)
+            : forward_device(net, net->d_stage_img[slot], cnt, net->d_stage_out[slot],
+                             net->d_stage_arg[slot], st);
     if (rc != CNN_OK) return rc;
     if (h_out)
       CNN_CUDA(cudaMemcpyAsync(h_out + done * kOut, net->d_stage_out[slot],
@@ -197,4 +205,14 @@ int cnn_forward_batched_host(cnn_net* net, const float* h_images, long n, float*
   return CNN_OK;
 }
 
+int cnn_forward_batched_host(cnn_net* net, const float* h_images, long n, float* h_out, int* h_argmax) {
+  return forward_host_impl(net, h_images, false, n, h_out, h_argmax);
+}
+
+int cnn_forward_batched_u8_host(cnn_net* net, const unsigned char* h_pixels, long n, float* h_out,
+                                int* h_argmax) {
+  return forward_host_impl(net, h_pixels, true, n, h_out, h_argmax);
+}
+
+extern "C" {
 }  // extern "C"

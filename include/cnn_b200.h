@@ -145,6 +145,15 @@ int cnn_forward_batched(cnn_net* net, const float* d_images, long n, float* d_ou
 int cnn_forward_batched_host(cnn_net* net, const float* h_images, long n, float* h_out,
                              int* h_argmax);
 
+/* The same two calls for uint8 pixels [n][28][28] -- the storage of the IDX files the reference's
+ * loader reads (mnist.h:79-160).  The kernel applies the reference's ingest, float(pixel / 255.0)
+ * (mnist.h:145, main.cu:57-65), on the fly, so results are bit-identical to the fp32 calls on the
+ * converted images while a quarter of the bytes cross PCIe and HBM. */
+int cnn_forward_batched_u8(cnn_net* net, const unsigned char* d_pixels, long n, float* d_out,
+                           int* d_argmax, void* stream);
+int cnn_forward_batched_u8_host(cnn_net* net, const unsigned char* h_pixels, long n, float* h_out,
+                                int* h_argmax);
+
 /* Device-side synthetic data (stands in for the MNIST files the reference reads, main.cu:30-33):
  * image i of the set 'seed' = strokes of uint8 values 128..255 on a zero canvas, stored as
  * float(uint8)/255 like mnist.h:145; label = hash % 10.  Bit-identical to the host generator in

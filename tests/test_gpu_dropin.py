@@ -1,0 +1,57 @@
+"""The reference's own program as the judge of the drop-in (GPU).
+
+The reference's unmodified main.cu is built twice (oracle/build_dropin.py): against the reference's
+layer.cu and against this repository's compat/layer.cu.  Both binaries, and the fused-kernel driver
+(driver.py), train and test on the same synthetic IDX files; their printed per-epoch errors and
+accuracies must agree."""
+import importlib.util
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _targets():
+    spec = importlib.util.spec_from_file_location("build_dropin", os.path.join(ROOT, "oracle", "build_dropin.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build_dropin()
+
+
+def _run(exe, cwd):
+    env = dict(os.environ)
+    env["LD_LIBRARY_PATH"] = "/usr/local/cuda/lib64:" + env.get("LD_LIBRARY_PATH", "")
+    r = subprocess.run([exe], cwd=cwd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    errs = [float(m) for m in re.findall(r"\d+: error: ([0-9.eE+-]+),", r.stdout)]
+    acc = float(re.search(r"Accuracy: ([0-9.eE+-]+)%", r.stdout).group(1))
+    return errs, acc
+
+
+def test_reference_main_runs_on_the_dropin_and_agrees(cuda, pkg, tmp_path):
+    targets = _targets()
+    if targets is None:
+        pytest.skip("reference program not built")
+    from hpcnn_b200 import driver, idx
+    n_train, n_test = 1500, 400
+    train = (pkg.synth.synth_pixels_u8(0, n_train), pkg.synth.synth_labels(0, n_train))
+    test = (pkg.synth.synth_pixels_u8(0, n_test, first_index=n_train),
+            pkg.synth.synth_labels(0, n_test, first_index=n_train))
+    idx.write_reference_data_dir(str(tmp_path), train, test)
+    ref_errs, ref_acc = _run(targets["reference"], str(tmp_path))
+    drop_errs, drop_acc = _run(targets["dropin"], str(tmp_path))
+    lines = []
+    fused_errs, fused_acc = driver.learn_and_test(str(tmp_path), out=lines.append)
+    print("reference", ref_errs, ref_acc, "| drop-in", drop_errs, drop_acc, "| fused", list(fused_errs), fused_acc)
+    assert len(ref_errs) == len(drop_errs) == len(fused_errs) == 5
+    # 7,500 sequential SGD steps: rounding compounds (the reference's atomics are themselves
+    # run-dependent), so the bar is 1e-3 relative on the printed epoch errors and 1 point of accuracy
+    assert np.allclose(drop_errs, ref_errs, rtol=1e-3)
+    assert np.allclose(fused_errs, ref_errs, rtol=1e-3)
+    assert abs(drop_acc - ref_acc) <= 1.0 and abs(fused_acc - ref_acc) <= 1.0
+    assert any(l.startswith("Accuracy: ") for l in lines) and lines[0] == "Learning"

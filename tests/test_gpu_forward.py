@@ -154,3 +154,24 @@ def test_device_generator_matches_host(cuda, pkg):
     h_img, h_lab = pkg.synth.synth_images(9, n, first_index=12345)
     assert np.array_equal(d_img.cpu().numpy(), h_img)
     assert np.array_equal(d_lab.cpu().numpy().astype(np.uint32), h_lab)
+
+
+@pytest.mark.parametrize("n", [1, 9, 1000, 8192 + 77])
+def test_uint8_input_is_bit_identical_to_fp32(cuda, pkg, params0, n):
+    """uint8 pixels through the in-kernel pixel/255.0 table == fp32 images through the fp32 kernel."""
+    pix = pkg.synth.synth_pixels_u8(26, n)
+    images = pkg.synth.u8_to_float(pix)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    out_f, arg_f = run_forward(cuda, net, images)
+    d_pix = cuda.from_numpy(pix).cuda()
+    d_out = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
+    d_arg = cuda.empty((n,), dtype=cuda.int32, device="cuda")
+    net.forward_u8(d_pix, n, d_out, d_arg)
+    cuda.cuda.synchronize()
+    assert net.status() == 0
+    assert np.array_equal(d_out.cpu().numpy(), out_f) and np.array_equal(d_arg.cpu().numpy(), arg_f)
+    h_out = np.empty((n, 10), dtype=np.float32)
+    h_arg = np.empty((n,), dtype=np.int32)
+    net.forward_u8_host(pix, n, h_out, h_arg)
+    assert np.array_equal(h_out, out_f) and np.array_equal(h_arg, arg_f)
