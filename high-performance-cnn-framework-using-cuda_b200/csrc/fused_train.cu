@@ -587,6 +587,10 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   float* d_mean = net->d_grad;
   int* d_ran = reinterpret_cast<int*>(net->d_grad + kNParamsPadded);
   const size_t smem = sizeof(TrSmem);
+  if (net->ps_cluster) {
+    if ((rc = launch_persample_cluster(net, d_images, d_labels, n, epochs, dt, threshold, d_mean, d_ran, st)) != CNN_OK)
+      return rc;
+  } else {
 #define CNN_LAUNCH_PS(FL)                                                                          \
   do {                                                                                             \
     if ((rc = set_smem_attr(k_train_persample<FL>, smem)) != CNN_OK) return rc;                    \
@@ -597,6 +601,7 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   else if (net->fast_sigmoid == 2) CNN_LAUNCH_PS(2);
   else CNN_LAUNCH_PS(0);
 #undef CNN_LAUNCH_PS
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_train_persample launch");
   CNN_CUDA(cudaStreamSynchronize(st));

@@ -135,6 +135,10 @@ int cnn_net_set_option(cnn_net* net, const char* key, int value) {
     net->fw_variant = value;
     return CNN_OK;
   }
+  if (std::strcmp(key, "persample_cluster") == 0) {
+    net->ps_cluster = value ? 1 : 0;
+    return CNN_OK;
+  }
   if (std::strcmp(key, "fast_sigmoid") == 0) {
     net->fast_sigmoid = (value == 2) ? 2 : (value ? 1 : 0);
     return CNN_OK;
