@@ -101,6 +101,15 @@ _PROTOTYPES = {
     "cnn_forward_batched_u8": (C.c_int, [_P, _P, C.c_long, _P, _P, _P]),
     "cnn_forward_batched_u8_host": (C.c_int, [_P, _P, C.c_long, _P, _P]),
     "cnn_synth_images": (C.c_int, [C.c_ulonglong, C.c_long, C.c_long, _P, _P, _P]),
+    "cnn_wide_param_count": (C.c_int, [C.c_int, C.c_int]),
+    "cnn_wide_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(_P)]),
+    "cnn_wide_destroy": (C.c_int, [_P]),
+    "cnn_wide_set_params": (C.c_int, [_P, _P]),
+    "cnn_wide_get_params": (C.c_int, [_P, _P]),
+    "cnn_wide_set_option": (C.c_int, [_P, C.c_char_p, C.c_int]),
+    "cnn_wide_forward": (C.c_int, [_P, _P, C.c_long, _P, _P, _P]),
+    "cnn_wide_grad_batch": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
+    "cnn_wide_apply_update": (C.c_int, [_P, _P, C.c_float, _P]),
     "cnn_copy_to_host": (C.c_int, [_P, _P, C.c_size_t]),
     "cnn_copy_to_device": (C.c_int, [_P, _P, C.c_size_t]),
     "cnn_grad_batch": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
@@ -374,6 +383,56 @@ class Net:
     def close(self) -> None:
         if getattr(self, "_h", None) is not None:
             load_library().cnn_net_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class WideNet:
+    """The widened variant of the same topology (H x H input, F maps; BASELINE config 5 is
+    H = 56, F = 64).  Parameters start at zero; set them with ``set_params``."""
+
+    def __init__(self, H: int = 56, F: int = 64):
+        lib = load_library()
+        self.H, self.F = H, F
+        self.n_params = int(lib.cnn_wide_param_count(H, F))
+        self.n_padded = ((self.n_params + 2 + 31) // 32) * 32
+        h = _P()
+        _check(lib.cnn_wide_create(H, F, C.byref(h)))
+        self._h = h
+
+    def set_params(self, params) -> None:
+        arr = np.ascontiguousarray(np.asarray(params, dtype=np.float32).reshape(-1))
+        if arr.size != self.n_params:
+            raise ValueError("parameter arena holds %d floats" % self.n_params)
+        _check(load_library().cnn_wide_set_params(self._h, _ptr(arr)))
+
+    def get_params(self) -> np.ndarray:
+        out = np.empty(self.n_params, dtype=np.float32)
+        _check(load_library().cnn_wide_get_params(self._h, _ptr(out)))
+        return out
+
+    def set_option(self, key: str, value: int) -> None:
+        _check(load_library().cnn_wide_set_option(self._h, key.encode(), int(value)))
+
+    def forward(self, d_images, n: int, d_out=None, d_argmax=None, stream=None) -> None:
+        _check(load_library().cnn_wide_forward(self._h, _ptr(d_images), int(n), _ptr(d_out), _ptr(d_argmax),
+                                               _stream(stream)))
+
+    def grad_batch(self, d_images, d_labels, n: int, d_grad, stream=None) -> None:
+        _check(load_library().cnn_wide_grad_batch(self._h, _ptr(d_images), _ptr(d_labels), int(n), _ptr(d_grad),
+                                                  _stream(stream)))
+
+    def apply_update(self, d_grad, scale: float, stream=None) -> None:
+        _check(load_library().cnn_wide_apply_update(self._h, _ptr(d_grad), float(scale), _stream(stream)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None:
+            load_library().cnn_wide_destroy(self._h)
             self._h = None
 
     def __del__(self):

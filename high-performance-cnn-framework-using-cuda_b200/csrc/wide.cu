@@ -1,0 +1,466 @@
+// Widened variant of the same topology (BASELINE config 5): input HxH, F maps of 5x5 (valid) ->
+// sigmoid -> ONE shared 4x4/stride-4 filter -> sigmoid -> FC F*P*P -> 10 -> sigmoid, with the
+// reference's update rule generalised as in the oracle: divisors (H-4)^2 for the conv gradient and
+// bias, F*P*P for the subsample bias (layer.cu:369, 389, 312 with 24 -> H-4 and 6*6*6 -> F*P*P).
+// The reference's own kernels cannot run this shape (fixed array types; N * thread_index overflows
+// int), so its check is the generalised oracle.
+//
+// This file is the fp32 SIMT path: batch-level kernels with the conv activations and conv deltas
+// kept in HBM between them (at 56x56 / 64 maps one image's activations are 692 KB, more than an
+// SM's shared memory).  All reductions are fixed-order (no atomics).
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "net.cuh"
+
+namespace cnn {
+
+struct WideDims {
+  int H, F, C, P, S;        // C = H-4, P = C/4, S = F*P*P
+  int o_wc, o_bc, o_ws, o_bs, o_wf, o_bf, n_params, n_padded;
+};
+
+static WideDims make_wide_dims(int H, int F) {
+  WideDims d;
+  d.H = H; d.F = F; d.C = H - 4; d.P = d.C / 4; d.S = F * d.P * d.P;
+  d.o_wc = 0; d.o_bc = d.o_wc + F * 25; d.o_ws = d.o_bc + F; d.o_bs = d.o_ws + 16;
+  d.o_wf = d.o_bs + 1; d.o_bf = d.o_wf + kOut * d.S; d.n_params = d.o_bf + kOut;
+  d.n_padded = ((d.n_params + 2 + 31) / 32) * 32;
+  return d;
+}
+
+constexpr int kWideFg = 8;       // filters per block in the forward conv
+constexpr int kWideGg = 4;       // filters per block in the conv weight gradient
+
+// ---- forward ---------------------------------------------------------------------------------
+// Block (image b, group of 8 maps): image in shared memory, thread = output position, 8 maps per
+// patch read.  Writes the conv ACTIVATIONS (sigmoid applied); pre-activations are never needed again
+// because sigmoid' = a (1 - a).
+template <int FLAVOR>
+__global__ void __launch_bounds__(256)
+k_wide_conv_fwd(WideDims d, const float* __restrict__ images, const float* __restrict__ params,
+                float* __restrict__ ac) {
+  extern __shared__ float sh[];
+  float* img = sh;                       // H*H
+  float* w = sh + d.H * d.H;             // 8 * 25
+  float* bias = w + kWideFg * 25;        // 8
+  const int b = blockIdx.x, f0 = blockIdx.y * kWideFg;
+  for (int i = threadIdx.x; i < d.H * d.H; i += blockDim.x) img[i] = images[(size_t)b * d.H * d.H + i];
+  for (int i = threadIdx.x; i < kWideFg * 25; i += blockDim.x)
+    w[i] = (f0 + i / 25 < d.F) ? params[d.o_wc + f0 * 25 + i] : 0.f;
+  if (threadIdx.x < kWideFg) bias[threadIdx.x] = (f0 + threadIdx.x < d.F) ? params[d.o_bc + f0 + threadIdx.x] : 0.f;
+  __syncthreads();
+  const int CC = d.C * d.C;
+  for (int o = threadIdx.x; o < CC; o += blockDim.x) {
+    const int y = o / d.C, x = o % d.C;
+    float acc[kWideFg];
+#pragma unroll
+    for (int g = 0; g < kWideFg; ++g) acc[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 5; ++j)
+#pragma unroll
+      for (int i = 0; i < 5; ++i) {
+        const float v = img[(y + i) * d.H + x + j];
+#pragma unroll
+        for (int g = 0; g < kWideFg; ++g) acc[g] = fmaf(w[g * 25 + i * 5 + j], v, acc[g]);
+      }
+#pragma unroll
+    for (int g = 0; g < kWideFg; ++g)
+      if (f0 + g < d.F) ac[((size_t)b * d.F + f0 + g) * CC + o] = sigmoidf<FLAVOR>(acc[g] + bias[g]);
+  }
+}
+
+// Thread = one subsample output (b, f, p, q).
+template <int FLAVOR>
+__global__ void k_wide_s1_fwd(WideDims d, long n, const float* __restrict__ ac,
+                              const float* __restrict__ params, float* __restrict__ as) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * d.S) return;
+  const int q = (int)(idx % d.P), p = (int)((idx / d.P) % d.P);
+  const long bf = idx / (d.P * d.P);
+  const float* src = ac + (size_t)bf * d.C * d.C + (4 * p) * d.C + 4 * q;
+  float z = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) z = fmaf(params[d.o_ws + i * 4 + j], src[i * d.C + j], z);
+  as[idx] = sigmoidf<FLAVOR>(z + params[d.o_bs]);
+}
+
+// Block = one image: FC, sigmoid, argmax, makeError, error norm.
+template <int FLAVOR>
+__global__ void __launch_bounds__(256)
+k_wide_fc_fwd(WideDims d, const float* __restrict__ as, const float* __restrict__ params,
+              const unsigned* __restrict__ labels, float* __restrict__ out, int* __restrict__ argmax,
+              float* __restrict__ delta_f, float* __restrict__ err) {
+  __shared__ float red[8][kOut];
+  __shared__ float o_s[kOut];
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* a = as + (size_t)b * d.S;
+  float acc[kOut];
+#pragma unroll
+  for (int k = 0; k < kOut; ++k) acc[k] = 0.f;
+  for (int s = threadIdx.x; s < d.S; s += blockDim.x) {
+    const float v = a[s];
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) acc[k] = fmaf(params[d.o_wf + (size_t)k * d.S + s], v, acc[k]);
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1)
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], m);
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) red[warp][k] = acc[k];
+  }
+  __syncthreads();
+  if (threadIdx.x < kOut) {
+    float z = 0.f;
+    for (int ww = 0; ww < 8; ++ww) z += red[ww][threadIdx.x];
+    const float o = sigmoidf<FLAVOR>(z + params[d.o_bf + threadIdx.x]);
+    o_s[threadIdx.x] = o;
+    if (out) out[(size_t)b * kOut + threadIdx.x] = o;
+    if (delta_f) delta_f[(size_t)b * kOut + threadIdx.x] = ((labels[b] == (unsigned)threadIdx.x) ? 1.0f : 0.0f) - o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int best = 0;
+    for (int k = 1; k < kOut; ++k)
+      if (o_s[best] < o_s[k]) best = k;
+    if (argmax) argmax[b] = best;
+    if (err) {
+      float ss = 0.f;
+      for (int k = 0; k < kOut; ++k) {
+        const float dlt = ((labels[b] == (unsigned)k) ? 1.0f : 0.0f) - o_s[k];
+        ss += dlt * dlt;
+      }
+      err[b] = sqrtf(ss);
+    }
+  }
+}
+
+// ---- backward --------------------------------------------------------------------------------
+// delta_s[b][s] = (sum_k Wf[k][s] delta_f[b][k]) * as (1 - as)
+__global__ void k_wide_bp_s1(WideDims d, long n, const float* __restrict__ as, const float* __restrict__ delta_f,
+                             const float* __restrict__ params, float* __restrict__ ds) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * d.S) return;
+  const long b = idx / d.S;
+  const int s = (int)(idx % d.S);
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < kOut; ++k) acc = fmaf(params[d.o_wf + (size_t)k * d.S + s], delta_f[b * kOut + k], acc);
+  const float a = as[idx];
+  ds[idx] = acc * a * (1.f - a);
+}
+
+// G_wf[k][s] = sum_b delta_f[b][k] as[b][s]   (thread = s, images in index order); also G_bf.
+__global__ void k_wide_grad_fc(WideDims d, long n, const float* __restrict__ as, const float* __restrict__ delta_f,
+                               float* __restrict__ G) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s < d.S) {
+    float acc[kOut];
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) acc[k] = 0.f;
+    for (long b = 0; b < n; ++b) {
+      const float v = as[b * d.S + s];
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) acc[k] = fmaf(delta_f[b * kOut + k], v, acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) G[d.o_wf + (size_t)k * d.S + s] = acc[k];
+  }
+  if (blockIdx.x == 0 && threadIdx.x < kOut) {
+    float acc = 0.f;
+    for (long b = 0; b < n; ++b) acc += delta_f[b * kOut + threadIdx.x];
+    G[d.o_bf + threadIdx.x] = acc;
+  }
+}
+
+// Per image: 16 subsample-filter gradient partials + bias partial -> part[b][17]; also writes the
+// conv deltas dc = Ws[i][j] * delta_s * a (1 - a) / (C*C).  Block = one image, thread strides over
+// (f, p, q).
+__global__ void __launch_bounds__(256)
+k_wide_bp_c1(WideDims d, const float* __restrict__ ac, const float* __restrict__ ds,
+             const float* __restrict__ params, float* __restrict__ dc, float* __restrict__ part) {
+  __shared__ float red[8][17];
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float inv_c = 1.0f / (float)(d.C * d.C), inv_s = 1.0f / (float)d.S;
+  float ws[16];
+#pragma unroll
+  for (int t = 0; t < 16; ++t) ws[t] = params[d.o_ws + t];
+  float acc[17];
+#pragma unroll
+  for (int t = 0; t < 17; ++t) acc[t] = 0.f;
+  for (int s = threadIdx.x; s < d.S; s += blockDim.x) {
+    const int q = s % d.P, p = (s / d.P) % d.P, f = s / (d.P * d.P);
+    const float dlt = ds[(size_t)b * d.S + s];
+    const size_t base = ((size_t)b * d.F + f) * d.C * d.C + (4 * p) * d.C + 4 * q;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = ac[base + i * d.C + j];
+        acc[i * 4 + j] = fmaf(dlt, a, acc[i * 4 + j]);
+        dc[base + i * d.C + j] = (ws[i * 4 + j] * dlt) * a * (1.f - a) * inv_c;
+      }
+    acc[16] += dlt * inv_s;
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1)
+#pragma unroll
+    for (int t = 0; t < 17; ++t) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], m);
+  if (lane == 0) {
+#pragma unroll
+    for (int t = 0; t < 17; ++t) red[warp][t] = acc[t];
+  }
+  __syncthreads();
+  if (threadIdx.x < 17) {
+    float sum = 0.f;
+    for (int ww = 0; ww < 8; ++ww) sum += red[ww][threadIdx.x];
+    part[(size_t)b * 17 + threadIdx.x] = sum;
+  }
+  // positions outside the 4P x 4P area (only when C is not a multiple of 4) get no delta
+  if (4 * d.P != d.C) {
+    for (int o = threadIdx.x; o < d.F * d.C * d.C; o += blockDim.x) {
+      const int x = o % d.C, y = (o / d.C) % d.C;
+      if (y >= 4 * d.P || x >= 4 * d.P) dc[(size_t)b * d.F * d.C * d.C + o] = 0.f;
+    }
+  }
+}
+
+// Conv weight gradient partial of one image for 4 maps: part[b][f][26] (25 taps + bias term).
+__global__ void __launch_bounds__(256)
+k_wide_grad_c1(WideDims d, const float* __restrict__ images, const float* __restrict__ dc,
+               float* __restrict__ part) {
+  extern __shared__ float sh[];
+  float* img = sh;                                  // H*H
+  float* red = sh + d.H * d.H;                      // 8 warps * 4 maps * 26
+  const int b = blockIdx.x, f0 = blockIdx.y * kWideGg;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < d.H * d.H; i += blockDim.x) img[i] = images[(size_t)b * d.H * d.H + i];
+  __syncthreads();
+  const int CC = d.C * d.C;
+  float acc[kWideGg][26];
+#pragma unroll
+  for (int g = 0; g < kWideGg; ++g)
+#pragma unroll
+    for (int t = 0; t < 26; ++t) acc[g][t] = 0.f;
+  for (int o = threadIdx.x; o < CC; o += blockDim.x) {
+    const int y = o / d.C, x = o % d.C;
+    float dv[kWideGg];
+#pragma unroll
+    for (int g = 0; g < kWideGg; ++g) {
+      dv[g] = (f0 + g < d.F) ? dc[((size_t)b * d.F + f0 + g) * CC + o] : 0.f;
+      acc[g][25] += dv[g];
+    }
+#pragma unroll
+    for (int i = 0; i < 5; ++i)
+#pragma unroll
+      for (int j = 0; j < 5; ++j) {
+        const float v = img[(y + i) * d.H + x + j];
+#pragma unroll
+        for (int g = 0; g < kWideGg; ++g) acc[g][i * 5 + j] = fmaf(dv[g], v, acc[g][i * 5 + j]);
+      }
+  }
+#pragma unroll
+  for (int g = 0; g < kWideGg; ++g)
+#pragma unroll
+    for (int t = 0; t < 26; ++t) {
+      float v = acc[g][t];
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+      if (lane == 0) red[(warp * kWideGg + g) * 26 + t] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < kWideGg * 26) {
+    const int g = threadIdx.x / 26, t = threadIdx.x % 26;
+    float sum = 0.f;
+    for (int ww = 0; ww < 8; ++ww) sum += red[(ww * kWideGg + g) * 26 + t];
+    if (f0 + g < d.F) part[((size_t)b * d.F + f0 + g) * 26 + t] = sum;
+  }
+}
+
+// Sum the per-image partials in image order into the arena-ordered gradient; G[n_params+1] = sum of
+// the per-image error norms; padding zeroed.
+__global__ void k_wide_reduce(WideDims d, long n, const float* __restrict__ part_c, const float* __restrict__ part_s,
+                              const float* __restrict__ err, float* __restrict__ G) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n_c = d.F * 26;
+  if (t < n_c) {
+    float sum = 0.f;
+    for (long b = 0; b < n; ++b) sum += part_c[(size_t)b * n_c + t];
+    const int f = t / 26, k = t % 26;
+    if (k < 25) G[d.o_wc + f * 25 + k] = sum; else G[d.o_bc + f] = sum;
+  } else if (t < n_c + 17) {
+    const int k = t - n_c;
+    float sum = 0.f;
+    for (long b = 0; b < n; ++b) sum += part_s[(size_t)b * 17 + k];
+    if (k < 16) G[d.o_ws + k] = sum; else G[d.o_bs] = sum;
+  } else if (t == n_c + 17) {
+    float sum = 0.f;
+    for (long b = 0; b < n; ++b) sum += err[b];
+    G[d.n_params + 1] = sum;
+    G[d.n_params] = 0.f;
+    for (int i = d.n_params + 2; i < d.n_padded; ++i) G[i] = 0.f;
+  }
+}
+
+__global__ void k_wide_update(int n_params, float* __restrict__ params, const float* __restrict__ G, float scale) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_params) params[i] = fmaf(scale, G[i], params[i]);
+}
+
+}  // namespace cnn
+
+using namespace cnn;
+
+struct cnn_wide {
+  WideDims d;
+  float* d_params = nullptr;
+  long cap = 0;                 // images the workspace holds
+  float *ac = nullptr, *dc = nullptr, *as = nullptr, *ds = nullptr, *delta_f = nullptr, *err = nullptr;
+  float *part_c = nullptr, *part_s = nullptr;
+  int flavour = 0;
+};
+
+static int wide_reserve(cnn_wide* w, long n) {
+  if (n <= w->cap) return CNN_OK;
+  float** bufs[] = {&w->ac, &w->dc, &w->as, &w->ds, &w->delta_f, &w->err, &w->part_c, &w->part_s};
+  for (float** p : bufs) { cudaFree(*p); *p = nullptr; }
+  w->cap = 0;
+  const WideDims& d = w->d;
+  const size_t fcc = (size_t)d.F * d.C * d.C;
+  CNN_CUDA(cudaMalloc(&w->ac, sizeof(float) * fcc * n));
+  CNN_CUDA(cudaMalloc(&w->dc, sizeof(float) * fcc * n));
+  CNN_CUDA(cudaMalloc(&w->as, sizeof(float) * (size_t)d.S * n));
+  CNN_CUDA(cudaMalloc(&w->ds, sizeof(float) * (size_t)d.S * n));
+  CNN_CUDA(cudaMalloc(&w->delta_f, sizeof(float) * kOut * n));
+  CNN_CUDA(cudaMalloc(&w->err, sizeof(float) * n));
+  CNN_CUDA(cudaMalloc(&w->part_c, sizeof(float) * (size_t)d.F * 26 * n));
+  CNN_CUDA(cudaMalloc(&w->part_s, sizeof(float) * 17 * n));
+  w->cap = n;
+  return CNN_OK;
+}
+
+template <int FL>
+static int wide_forward_impl(cnn_wide* w, const float* d_images, const unsigned* d_labels, long n, float* d_out,
+                             int* d_argmax, bool training, cudaStream_t st) {
+  const WideDims& d = w->d;
+  const size_t smem = sizeof(float) * ((size_t)d.H * d.H + kWideFg * 25 + kWideFg);
+  CNN_CUDA(cudaFuncSetAttribute(k_wide_conv_fwd<FL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_wide_conv_fwd<FL><<<dim3((unsigned)n, (d.F + kWideFg - 1) / kWideFg), 256, smem, st>>>(d, d_images, w->d_params, w->ac);
+  const long ns = n * d.S;
+  k_wide_s1_fwd<FL><<<(unsigned)((ns + 255) / 256), 256, 0, st>>>(d, n, w->ac, w->d_params, w->as);
+  k_wide_fc_fwd<FL><<<(unsigned)n, 256, 0, st>>>(d, w->as, w->d_params, d_labels, d_out, d_argmax,
+                                                 training ? w->delta_f : nullptr, training ? w->err : nullptr);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "wide forward launch");
+  return CNN_OK;
+}
+
+static int wide_forward_dispatch(cnn_wide* w, const float* d_images, const unsigned* d_labels, long n, float* d_out,
+                                 int* d_argmax, bool training, cudaStream_t st) {
+  switch (w->flavour) {
+    case 1: return wide_forward_impl<1>(w, d_images, d_labels, n, d_out, d_argmax, training, st);
+    case 2: return wide_forward_impl<2>(w, d_images, d_labels, n, d_out, d_argmax, training, st);
+    default: return wide_forward_impl<0>(w, d_images, d_labels, n, d_out, d_argmax, training, st);
+  }
+}
+
+extern "C" {
+
+int cnn_wide_param_count(int H, int F) {
+  if (H < 8 || F < 1) return -1;
+  return make_wide_dims(H, F).n_params;
+}
+
+int cnn_wide_create(int H, int F, cnn_wide** out) {
+  CNN_REQUIRE(out != nullptr, "cnn_wide_create: out is NULL");
+  *out = nullptr;
+  CNN_REQUIRE(H >= 8 && H <= 128 && F >= 1 && F <= 1024, "cnn_wide_create: unsupported shape");
+  cnn_wide* w = new (std::nothrow) cnn_wide();
+  CNN_REQUIRE(w != nullptr, "cnn_wide_create: out of host memory");
+  w->d = make_wide_dims(H, F);
+  cudaError_t e = cudaMalloc(&w->d_params, sizeof(float) * w->d.n_padded);
+  if (e == cudaSuccess) e = cudaMemset(w->d_params, 0, sizeof(float) * w->d.n_padded);
+  if (e != cudaSuccess) { delete w; return cuda_fail(e, "cnn_wide_create"); }
+  *out = w;
+  return CNN_OK;
+}
+
+int cnn_wide_destroy(cnn_wide* w) {
+  if (!w) return CNN_OK;
+  float* bufs[] = {w->d_params, w->ac, w->dc, w->as, w->ds, w->delta_f, w->err, w->part_c, w->part_s};
+  for (float* p : bufs) cudaFree(p);
+  delete w;
+  return CNN_OK;
+}
+
+int cnn_wide_set_params(cnn_wide* w, const float* h_params) {
+  CNN_REQUIRE(w && h_params, "cnn_wide_set_params: NULL argument");
+  CNN_CUDA(cudaMemcpy(w->d_params, h_params, sizeof(float) * w->d.n_params, cudaMemcpyHostToDevice));
+  return CNN_OK;
+}
+
+int cnn_wide_get_params(cnn_wide* w, float* h_params) {
+  CNN_REQUIRE(w && h_params, "cnn_wide_get_params: NULL argument");
+  CNN_CUDA(cudaMemcpy(h_params, w->d_params, sizeof(float) * w->d.n_params, cudaMemcpyDeviceToHost));
+  return CNN_OK;
+}
+
+int cnn_wide_set_option(cnn_wide* w, const char* key, int value) {
+  CNN_REQUIRE(w && key, "cnn_wide_set_option: NULL argument");
+  if (std::strcmp(key, "fast_sigmoid") == 0) { w->flavour = (value == 2) ? 2 : (value ? 1 : 0); return CNN_OK; }
+  set_error("cnn_wide_set_option: unknown option '%s'", key);
+  return CNN_ERR_INVALID;
+}
+
+int cnn_wide_forward(cnn_wide* w, const float* d_images, long n, float* d_out, int* d_argmax, void* stream) {
+  CNN_REQUIRE(w != nullptr, "cnn_wide_forward: NULL handle");
+  CNN_REQUIRE(n >= 0 && n <= 65535L * 32, "cnn_wide_forward: bad image count");
+  if (n == 0) return CNN_OK;
+  CNN_REQUIRE(d_images != nullptr, "cnn_wide_forward: NULL images");
+  int rc = wide_reserve(w, n);
+  if (rc != CNN_OK) return rc;
+  return wide_forward_dispatch(w, d_images, nullptr, n, d_out, d_argmax, false, as_stream(stream));
+}
+
+int cnn_wide_grad_batch(cnn_wide* w, const float* d_images, const unsigned int* d_labels, long n, float* d_grad,
+                        void* stream) {
+  CNN_REQUIRE(w && d_grad, "cnn_wide_grad_batch: NULL argument");
+  CNN_REQUIRE(n >= 0 && n <= 65535L * 32, "cnn_wide_grad_batch: bad image count");
+  cudaStream_t st = as_stream(stream);
+  const WideDims& d = w->d;
+  if (n == 0) {
+    CNN_CUDA(cudaMemsetAsync(d_grad, 0, sizeof(float) * d.n_padded, st));
+    return CNN_OK;
+  }
+  CNN_REQUIRE(d_images && d_labels, "cnn_wide_grad_batch: NULL images or labels");
+  int rc = wide_reserve(w, n);
+  if (rc != CNN_OK) return rc;
+  if ((rc = wide_forward_dispatch(w, d_images, d_labels, n, nullptr, nullptr, true, st)) != CNN_OK) return rc;
+  const long ns = n * d.S;
+  k_wide_bp_s1<<<(unsigned)((ns + 255) / 256), 256, 0, st>>>(d, n, w->as, w->delta_f, w->d_params, w->ds);
+  k_wide_grad_fc<<<(d.S + 127) / 128, 128, 0, st>>>(d, n, w->as, w->delta_f, d_grad);
+  k_wide_bp_c1<<<(unsigned)n, 256, 0, st>>>(d, w->ac, w->ds, w->d_params, w->dc, w->part_s);
+  const size_t smem = sizeof(float) * ((size_t)d.H * d.H + 8 * kWideGg * 26);
+  CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_wide_grad_c1<<<dim3((unsigned)n, (d.F + kWideGg - 1) / kWideGg), 256, smem, st>>>(d, d_images, w->dc, w->part_c);
+  const int n_red = d.F * 26 + 18;
+  k_wide_reduce<<<(n_red + 127) / 128, 128, 0, st>>>(d, n, w->part_c, w->part_s, w->err, d_grad);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "wide backward launch");
+  return CNN_OK;
+}
+
+int cnn_wide_apply_update(cnn_wide* w, const float* d_grad, float scale, void* stream) {
+  CNN_REQUIRE(w && d_grad, "cnn_wide_apply_update: NULL argument");
+  k_wide_update<<<(w->d.n_params + 255) / 256, 256, 0, as_stream(stream)>>>(w->d.n_params, w->d_params, d_grad, scale);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "k_wide_update launch");
+  return CNN_OK;
+}
+
+}  // extern "C"

@@ -214,6 +214,31 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
 int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const unsigned int* d_labels,
                            long n, float* d_grad, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Widened variant of the same topology: input HxH, F maps of 5x5 -> sigmoid -> one shared 4x4 /
+ * stride-4 filter -> sigmoid -> FC F*P*P -> 10 -> sigmoid (C = H-4, P = C/4).  The reference's
+ * kernels are fixed to 28x28 / 6 maps (layer.h:45-62); this is the same operator sequence
+ * (layer.cu:116-399 in main.cu's order) with its literals generalised: divisors (H-4)^2 for the conv
+ * gradient and conv bias, F*P*P for the subsample bias.  Parameter arena:
+ * [Wc F*25 | bc F | Ws 16 | bs 1 | Wf 10*F*P*P | bf 10]; gradient vectors hold the arena, then 0, then
+ * the sum of error norms, zero-padded to a multiple of 32 floats.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct cnn_wide cnn_wide;
+int cnn_wide_param_count(int H, int F);
+int cnn_wide_create(int H, int F, cnn_wide** out);       /* parameters start at zero */
+int cnn_wide_destroy(cnn_wide* w);
+int cnn_wide_set_params(cnn_wide* w, const float* h_params);
+int cnn_wide_get_params(cnn_wide* w, float* h_params);
+/* "fast_sigmoid" 0 / 1 / 2 as for cnn_net; "conv" 0 = fp32 SIMT convolution. */
+int cnn_wide_set_option(cnn_wide* w, const char* key, int value);
+/* forward_pass + classify for n images [n][H][H] -> d_out [n][10], d_argmax [n] (either may be NULL). */
+int cnn_wide_forward(cnn_wide* w, const float* d_images, long n, float* d_out, int* d_argmax, void* stream);
+/* forward + makeError + back_pass for n images at fixed parameters: summed gradient as for
+ * cnn_grad_batch. */
+int cnn_wide_grad_batch(cnn_wide* w, const float* d_images, const unsigned int* d_labels, long n,
+                        float* d_grad, void* stream);
+int cnn_wide_apply_update(cnn_wide* w, const float* d_grad, float scale, void* stream);
+
 /* Blocking copies between host and device memory (for bindings without a CUDA runtime of their own). */
 int cnn_copy_to_host(void* h_dst, const void* d_src, size_t bytes);
 int cnn_copy_to_device(void* d_dst, const void* h_src, size_t bytes);

@@ -1,0 +1,112 @@
+"""Widened configuration (BASELINE config 5: 56x56 input, 64 maps) on the GPU against the generalised
+oracle; the same kernels at 28x28 / 6 maps against the fused path of the reference net."""
+import numpy as np
+import pytest
+
+from conftest import rel_err, scaled_err
+
+pytestmark = pytest.mark.gpu
+
+
+def wide_inputs(n, H, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.random((n, H, H), dtype=np.float32)
+    x[rng.random((n, H, H)) < 0.8] = 0.0          # MNIST-like sparsity
+    labels = rng.integers(0, 10, n).astype(np.uint32)
+    return x, labels
+
+
+def wide_params(ob, H, F, seed):
+    rng = np.random.default_rng(seed)
+    n = ob.param_count(H, F)
+    p = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    S = F * ((H - 4) // 4) ** 2
+    p[F * 25 + F + 17: F * 25 + F + 17 + 10 * S] *= np.float32(6.0 / np.sqrt(S))   # keep the FC out of saturation
+    return p
+
+
+def blocks(H, F):
+    S = F * ((H - 4) // 4) ** 2
+    o = [0, F * 25, F * 25 + F, F * 25 + F + 16, F * 25 + F + 17, F * 25 + F + 17 + 10 * S, F * 25 + F + 27 + 10 * S]
+    return dict(zip(["Wc", "bc", "Ws", "bs", "Wf", "bf"], zip(o[:-1], o[1:])))
+
+
+@pytest.mark.parametrize("H,F,n", [(56, 64, 6), (56, 64, 1), (28, 6, 40), (32, 5, 9)])
+def test_wide_forward_and_gradient_match_oracle(cuda, pkg, ob, H, F, n):
+    x, labels = wide_inputs(n, H, 1)
+    params = wide_params(ob, H, F, 2)
+    net = pkg.WideNet(H, F)
+    assert net.n_params == ob.param_count(H, F)
+    net.set_params(params)
+    d_x = cuda.from_numpy(x).cuda()
+    d_lab = cuda.from_numpy(labels.astype(np.int32)).cuda()
+    d_out = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
+    d_arg = cuda.empty((n,), dtype=cuda.int32, device="cuda")
+    net.forward(d_x, n, d_out, d_arg)
+    cuda.cuda.synchronize()
+    ref_out, ref_arg = ob.forward_batch(params, x, H=H, F=F)
+    assert rel_err(d_out.cpu().numpy(), ref_out) < 1e-5
+    top2 = np.sort(ref_out, axis=1)
+    ok = (top2[:, -1] - top2[:, -2]) > 1e-5 * top2[:, -1]
+    assert np.array_equal(d_arg.cpu().numpy()[ok], ref_arg[ok])
+    d_g = cuda.full((net.n_padded,), 9.0, dtype=cuda.float32, device="cuda")
+    net.grad_batch(d_x, d_lab, n, d_g)
+    cuda.cuda.synchronize()
+    g = d_g.cpu().numpy()
+    G, err = ob.grad_batch(params, x, labels, H=H, F=F)
+    for name, (lo, hi) in blocks(H, F).items():
+        assert scaled_err(g[lo:hi], G[lo:hi]) < 1e-5, name
+    assert abs(g[net.n_params + 1] - err) < 1e-5 * max(err, 1.0)
+    assert g[net.n_params] == 0 and not g[net.n_params + 2:].any()
+    # one minibatch step
+    net.apply_update(d_g, 0.1 / n)
+    cuda.cuda.synchronize()
+    want = ob.apply_update(params, G, 0.1, n)
+    assert scaled_err(net.get_params(), want) < 1e-5
+
+
+def test_wide_kernels_agree_with_the_fused_reference_net(cuda, pkg, params0):
+    """At 28x28 / 6 maps the widened path and the fused path are two implementations of one net."""
+    n = 300
+    images, labels = pkg.synth.synth_images(61, n)
+    d_x = cuda.from_numpy(images).cuda()
+    d_lab = cuda.from_numpy(labels.astype(np.int32)).cuda()
+    wide = pkg.WideNet(28, 6)
+    wide.set_params(params0)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    o1 = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
+    o2 = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
+    wide.forward(d_x, n, o1, None)
+    net.forward(d_x, n, o2, None)
+    g1 = cuda.zeros(wide.n_padded, dtype=cuda.float32, device="cuda")
+    g2 = cuda.zeros(2368, dtype=cuda.float32, device="cuda")
+    wide.grad_batch(d_x, d_lab, n, g1)
+    net.grad_batch(d_x, d_lab, n, g2)
+    cuda.cuda.synchronize()
+    assert rel_err(o1.cpu().numpy(), o2.cpu().numpy()) < 1e-5
+    assert scaled_err(g1.cpu().numpy()[:2343], g2.cpu().numpy()[:2343]) < 1e-5
+
+
+def test_wide_full_batch_runs_and_is_deterministic(cuda, pkg, ob):
+    """BASELINE config 5 size: batch 1,024 of 56x56 images, forward + backward twice, bit-identical."""
+    H, F, n = 56, 64, 1024
+    x, labels = wide_inputs(n, H, 3)
+    net = pkg.WideNet(H, F)
+    net.set_params(wide_params(ob, H, F, 4))
+    d_x = cuda.from_numpy(x).cuda()
+    d_lab = cuda.from_numpy(labels.astype(np.int32)).cuda()
+    ga = cuda.zeros(net.n_padded, dtype=cuda.float32, device="cuda")
+    gb = cuda.zeros(net.n_padded, dtype=cuda.float32, device="cuda")
+    net.grad_batch(d_x, d_lab, n, ga)
+    net.grad_batch(d_x, d_lab, n, gb)
+    cuda.cuda.synchronize()
+    assert cuda.equal(ga, gb) and bool(cuda.isfinite(ga).all())
+    # additivity over shards (what data-parallel training relies on)
+    g1 = cuda.zeros(net.n_padded, dtype=cuda.float32, device="cuda")
+    g2 = cuda.zeros(net.n_padded, dtype=cuda.float32, device="cuda")
+    net.grad_batch(d_x[:512], d_lab[:512], 512, g1)
+    net.grad_batch(d_x[512:], d_lab[512:], 512, g2)
+    cuda.cuda.synchronize()
+    s = (g1.double() + g2.double()).cpu().numpy()
+    assert scaled_err(ga.cpu().numpy()[:net.n_params], s[:net.n_params]) < 1e-5
