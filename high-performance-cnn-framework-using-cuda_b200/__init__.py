@@ -107,6 +107,7 @@ _PROTOTYPES = {
     "cnn_wide_set_params": (C.c_int, [_P, _P]),
     "cnn_wide_get_params": (C.c_int, [_P, _P]),
     "cnn_wide_set_option": (C.c_int, [_P, C.c_char_p, C.c_int]),
+    "cnn_wide_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "cnn_wide_forward": (C.c_int, [_P, _P, C.c_long, _P, _P, _P]),
     "cnn_wide_grad_batch": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
     "cnn_wide_apply_update": (C.c_int, [_P, _P, C.c_float, _P]),
@@ -418,6 +419,11 @@ class WideNet:
 
     def set_option(self, key: str, value: int) -> None:
         _check(load_library().cnn_wide_set_option(self._h, key.encode(), int(value)))
+
+    def status(self) -> int:
+        s = C.c_int(0)
+        _check(load_library().cnn_wide_status(self._h, C.byref(s)))
+        return s.value
 
     def forward(self, d_images, n: int, d_out=None, d_argmax=None, stream=None) -> None:
         _check(load_library().cnn_wide_forward(self._h, _ptr(d_images), int(n), _ptr(d_out), _ptr(d_argmax),

@@ -12,23 +12,9 @@
 #include <new>
 #include <vector>
 
-#include "net.cuh"
+#include "wide.cuh"
 
 namespace cnn {
-
-struct WideDims {
-  int H, F, C, P, S;        // C = H-4, P = C/4, S = F*P*P
-  int o_wc, o_bc, o_ws, o_bs, o_wf, o_bf, n_params, n_padded;
-};
-
-static WideDims make_wide_dims(int H, int F) {
-  WideDims d;
-  d.H = H; d.F = F; d.C = H - 4; d.P = d.C / 4; d.S = F * d.P * d.P;
-  d.o_wc = 0; d.o_bc = d.o_wc + F * 25; d.o_ws = d.o_bc + F; d.o_bs = d.o_ws + 16;
-  d.o_wf = d.o_bs + 1; d.o_bf = d.o_wf + kOut * d.S; d.n_params = d.o_bf + kOut;
-  d.n_padded = ((d.n_params + 2 + 31) / 32) * 32;
-  return d;
-}
 
 constexpr int kWideFg = 8;       // filters per block in the forward conv
 constexpr int kWideGg = 4;       // filters per block in the conv weight gradient
@@ -316,15 +302,6 @@ __global__ void k_wide_update(int n_params, float* __restrict__ params, const fl
 
 using namespace cnn;
 
-struct cnn_wide {
-  WideDims d;
-  float* d_params = nullptr;
-  long cap = 0;                 // images the workspace holds
-  float *ac = nullptr, *dc = nullptr, *as = nullptr, *ds = nullptr, *delta_f = nullptr, *err = nullptr;
-  float *part_c = nullptr, *part_s = nullptr;
-  int flavour = 0;
-};
-
 static int wide_reserve(cnn_wide* w, long n) {
   if (n <= w->cap) return CNN_OK;
   float** bufs[] = {&w->ac, &w->dc, &w->as, &w->ds, &w->delta_f, &w->err, &w->part_c, &w->part_s};
@@ -350,7 +327,12 @@ static int wide_forward_impl(cnn_wide* w, const float* d_images, const unsigned*
   const WideDims& d = w->d;
   const size_t smem = sizeof(float) * ((size_t)d.H * d.H + kWideFg * 25 + kWideFg);
   CNN_CUDA(cudaFuncSetAttribute(k_wide_conv_fwd<FL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  k_wide_conv_fwd<FL><<<dim3((unsigned)n, (d.F + kWideFg - 1) / kWideFg), 256, smem, st>>>(d, d_images, w->d_params, w->ac);
+  if (w->conv_mode > 0 && wide_conv_tc_supported(d)) {
+    const int rc = wide_conv_fwd_tc(w, d_images, n, st);
+    if (rc != CNN_OK) return rc;
+  } else {
+    k_wide_conv_fwd<FL><<<dim3((unsigned)n, (d.F + kWideFg - 1) / kWideFg), 256, smem, st>>>(d, d_images, w->d_params, w->ac);
+  }
   const long ns = n * d.S;
   k_wide_s1_fwd<FL><<<(unsigned)((ns + 255) / 256), 256, 0, st>>>(d, n, w->ac, w->d_params, w->as);
   k_wide_fc_fwd<FL><<<(unsigned)n, 256, 0, st>>>(d, w->as, w->d_params, d_labels, d_out, d_argmax,
@@ -385,6 +367,8 @@ int cnn_wide_create(int H, int F, cnn_wide** out) {
   w->d = make_wide_dims(H, F);
   cudaError_t e = cudaMalloc(&w->d_params, sizeof(float) * w->d.n_padded);
   if (e == cudaSuccess) e = cudaMemset(w->d_params, 0, sizeof(float) * w->d.n_padded);
+  if (e == cudaSuccess) e = cudaMalloc(&w->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(w->d_status, 0, sizeof(int));
   if (e != cudaSuccess) { delete w; return cuda_fail(e, "cnn_wide_create"); }
   *out = w;
   return CNN_OK;
@@ -394,6 +378,7 @@ int cnn_wide_destroy(cnn_wide* w) {
   if (!w) return CNN_OK;
   float* bufs[] = {w->d_params, w->ac, w->dc, w->as, w->ds, w->delta_f, w->err, w->part_c, w->part_s};
   for (float* p : bufs) cudaFree(p);
+  cudaFree(w->d_status);
   delete w;
   return CNN_OK;
 }
@@ -413,8 +398,26 @@ int cnn_wide_get_params(cnn_wide* w, float* h_params) {
 int cnn_wide_set_option(cnn_wide* w, const char* key, int value) {
   CNN_REQUIRE(w && key, "cnn_wide_set_option: NULL argument");
   if (std::strcmp(key, "fast_sigmoid") == 0) { w->flavour = (value == 2) ? 2 : (value ? 1 : 0); return CNN_OK; }
+  if (std::strcmp(key, "conv") == 0) {
+    CNN_REQUIRE(value >= 0 && value <= 2, "cnn_wide_set_option: conv is 0 (fp32 SIMT), 1 (tf32 tensor cores) or 2 (3 x tf32)");
+    w->conv_mode = value;
+    return CNN_OK;
+  }
   set_error("cnn_wide_set_option: unknown option '%s'", key);
   return CNN_ERR_INVALID;
+}
+
+int cnn_wide_status(cnn_wide* w, int* status) {
+  CNN_REQUIRE(w && status, "cnn_wide_status: NULL argument");
+  CNN_CUDA(cudaDeviceSynchronize());
+  CNN_CUDA(cudaMemcpy(status, w->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status != 0) {
+    set_error("a bounded device-side wait ran out (status %d)", *status);
+    int zero = 0;
+    CNN_CUDA(cudaMemcpy(w->d_status, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    return CNN_ERR_TIMEOUT;
+  }
+  return CNN_OK;
 }
 
 int cnn_wide_forward(cnn_wide* w, const float* d_images, long n, float* d_out, int* d_argmax, void* stream) {

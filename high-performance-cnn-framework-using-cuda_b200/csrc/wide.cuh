@@ -1,0 +1,41 @@
+// Shared definitions of the widened configuration (wide.cu: fp32 SIMT kernels and the C ABI;
+// wide_tc.cu: tcgen05 tensor-core convolution).
+#pragma once
+
+#include "net.cuh"
+
+namespace cnn {
+
+struct WideDims {
+  int H, F, C, P, S;        // C = H-4, P = C/4, S = F*P*P
+  int o_wc, o_bc, o_ws, o_bs, o_wf, o_bf, n_params, n_padded;
+};
+
+inline WideDims make_wide_dims(int H, int F) {
+  WideDims d;
+  d.H = H; d.F = F; d.C = H - 4; d.P = d.C / 4; d.S = F * d.P * d.P;
+  d.o_wc = 0; d.o_bc = d.o_wc + F * 25; d.o_ws = d.o_bc + F; d.o_bs = d.o_ws + 16;
+  d.o_wf = d.o_bs + 1; d.o_bf = d.o_wf + kOut * d.S; d.n_params = d.o_bf + kOut;
+  d.n_padded = ((d.n_params + 2 + 31) / 32) * 32;
+  return d;
+}
+
+}  // namespace cnn
+
+struct cnn_wide {
+  cnn::WideDims d;
+  float* d_params = nullptr;
+  long cap = 0;                 // images the workspace holds
+  float *ac = nullptr, *dc = nullptr, *as = nullptr, *ds = nullptr, *delta_f = nullptr, *err = nullptr;
+  float *part_c = nullptr, *part_s = nullptr;
+  int flavour = 0;
+  int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)
+  int* d_status = nullptr;      // bounded-wait status word
+};
+
+
+namespace cnn {
+bool wide_conv_tc_supported(const WideDims& d);
+// Conv + bias + sigmoid on the tensor cores: writes w->ac for n images.
+int wide_conv_fwd_tc(cnn_wide* w, const float* d_images, long n, cudaStream_t st);
+}  // namespace cnn

@@ -229,8 +229,12 @@ int cnn_wide_create(int H, int F, cnn_wide** out);       /* parameters start at 
 int cnn_wide_destroy(cnn_wide* w);
 int cnn_wide_set_params(cnn_wide* w, const float* h_params);
 int cnn_wide_get_params(cnn_wide* w, float* h_params);
-/* "fast_sigmoid" 0 / 1 / 2 as for cnn_net; "conv" 0 = fp32 SIMT convolution. */
+/* "fast_sigmoid" 0 / 1 / 2 as for cnn_net; "conv": 0 = fp32 SIMT convolution, 1 = implicit GEMM on the
+ * tf32 tensor cores (tcgen05, about 1e-3 relative), 2 = the same in three tf32 passes (hi*hi + lo*hi +
+ * hi*lo, fp32-level accuracy).  Tensor-core modes need F to be a multiple of 16, at most 256. */
 int cnn_wide_set_option(cnn_wide* w, const char* key, int value);
+/* As cnn_net_status. */
+int cnn_wide_status(cnn_wide* w, int* status);
 /* forward_pass + classify for n images [n][H][H] -> d_out [n][10], d_argmax [n] (either may be NULL). */
 int cnn_wide_forward(cnn_wide* w, const float* d_images, long n, float* d_out, int* d_argmax, void* stream);
 /* forward + makeError + back_pass for n images at fixed parameters: summed gradient as for

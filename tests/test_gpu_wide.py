@@ -110,3 +110,30 @@ def test_wide_full_batch_runs_and_is_deterministic(cuda, pkg, ob):
     cuda.cuda.synchronize()
     s = (g1.double() + g2.double()).cpu().numpy()
     assert scaled_err(ga.cpu().numpy()[:net.n_params], s[:net.n_params]) < 1e-5
+
+
+@pytest.mark.parametrize("mode,tol", [(2, 1e-5), (1, 3e-3)])
+@pytest.mark.parametrize("H,F,n", [(56, 64, 1), (56, 64, 5), (28, 16, 33)])
+def test_tensor_core_conv_matches_oracle(cuda, pkg, ob, H, F, n, mode, tol):
+    """conv = 2: three tf32 passes on tcgen05 keep the 1e-5 bar; conv = 1: one pass, tf32 accuracy."""
+    x, labels = wide_inputs(n, H, 5)
+    params = wide_params(ob, H, F, 6)
+    net = pkg.WideNet(H, F)
+    net.set_params(params)
+    net.set_option("conv", mode)
+    d_x = cuda.from_numpy(x).cuda()
+    d_lab = cuda.from_numpy(labels.astype(np.int32)).cuda()
+    d_out = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
+    net.forward(d_x, n, d_out, None)
+    cuda.cuda.synchronize()
+    assert net.status() == 0
+    ref_out, _ = ob.forward_batch(params, x, H=H, F=F)
+    assert rel_err(d_out.cpu().numpy(), ref_out) < tol
+    d_g = cuda.zeros(net.n_padded, dtype=cuda.float32, device="cuda")
+    net.grad_batch(d_x, d_lab, n, d_g)
+    cuda.cuda.synchronize()
+    assert net.status() == 0
+    G, _ = ob.grad_batch(params, x, labels, H=H, F=F)
+    g = d_g.cpu().numpy()
+    for name, (lo, hi) in blocks(H, F).items():
+        assert scaled_err(g[lo:hi], G[lo:hi]) < tol * (1 if mode == 2 else 10), name
