@@ -309,6 +309,53 @@ def run_ours(args):
     n_sm = torch.cuda.get_device_properties(local_rank).multi_processor_count
     fp32_peak = n_sm * 128 * 2 * sm_clock_ghz * 1e9
 
+    def run_wide_leg(modes=((0, "fp32_simt"), (2, "tf32x3_tcgen05"), (1, "tf32_tcgen05")), steps=5):
+        """BASELINE config 5: widened net (56x56 input, 64 maps), batch 1,024 per GPU, fwd+bwd+update."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wide_batch = 1024
+        wnet = pkg.WideNet(56, 64)
+        rng = np.random.default_rng(4)
+        wp = rng.uniform(-0.5, 0.5, wnet.n_params).astype(np.float32)
+        wp[64 * 25 + 64 + 17: 64 * 25 + 64 + 17 + 10 * 10816] *= np.float32(6.0 / np.sqrt(10816.0))
+        d_wimg = (torch.rand((wide_batch, 56, 56), device="cuda", generator=torch.Generator("cuda").manual_seed(4 + rank))
+                  * (torch.rand((wide_batch, 56, 56), device="cuda") < 0.2)).contiguous()
+        d_wlab = torch.randint(0, 10, (wide_batch,), dtype=torch.int32, device="cuda")
+        d_wgrad = torch.zeros(wnet.n_padded, dtype=torch.float32, device="cuda")
+        wide = {}
+        for mode, name in modes:
+            wnet.set_params(wp)
+            wnet.set_option("conv", mode)
+
+            def wstep():
+                wnet.grad_batch(d_wimg, d_wlab, wide_batch, d_wgrad, stream)
+                if world > 1:
+                    dist.all_reduce(d_wgrad)
+                wnet.apply_update(d_wgrad, 0.1 / (wide_batch * world), stream)
+
+            wstep()
+            barrier()
+            e0.record(stream)
+            for _ in range(steps):
+                wstep()
+            e1.record(stream)
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+            wide[name] = {"images_per_s": wide_batch * world / (ms * 1e-3), "ms_per_step": ms,
+                          "tflops": 18992896.0 * wide_batch * world / (ms * 1e-3) / 1e12}
+        assert wnet.status() == 0
+        return {"what": "BASELINE config 5: 56x56 input, 64 maps, batch 1,024 per GPU, "
+                                            "fwd+bwd+update" + (", NCCL all-reduce of 109,856 floats" if world > 1 else ""),
+                                    "conv": wide}
+
+    if args.only_wide:
+        res = run_wide_leg(modes=((args.only_wide - 1, "conv_mode_%d" % (args.only_wide - 1)),), steps=args.steps)
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"only_wide": True, "train_wide_cfg5": res}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     if args.only_forward:
         # profiling mode: the forward launches only (used under ncu); prints a reduced line
         sampler.stop()
@@ -406,41 +453,7 @@ def run_ours(args):
                                         "mean_err": float(mean_err[0]),
                                         "what": "BASELINE config 1: per-sample SGD in file order, one persistent block (does not shard)"}
         barrier()
-        # BASELINE config 5: widened net (56x56 input, 64 maps), batch 1,024 per GPU, fwd+bwd+update
-        wide_batch = 1024
-        wnet = pkg.WideNet(56, 64)
-        rng = np.random.default_rng(4)
-        wp = rng.uniform(-0.5, 0.5, wnet.n_params).astype(np.float32)
-        wp[64 * 25 + 64 + 17: 64 * 25 + 64 + 17 + 10 * 10816] *= np.float32(6.0 / np.sqrt(10816.0))
-        d_wimg = (torch.rand((wide_batch, 56, 56), device="cuda", generator=torch.Generator("cuda").manual_seed(4 + rank))
-                  * (torch.rand((wide_batch, 56, 56), device="cuda") < 0.2)).contiguous()
-        d_wlab = torch.randint(0, 10, (wide_batch,), dtype=torch.int32, device="cuda")
-        d_wgrad = torch.zeros(wnet.n_padded, dtype=torch.float32, device="cuda")
-        wide = {}
-        for mode, name in ((0, "fp32_simt"), (2, "tf32x3_tcgen05"), (1, "tf32_tcgen05")):
-            wnet.set_params(wp)
-            wnet.set_option("conv", mode)
-
-            def wstep():
-                wnet.grad_batch(d_wimg, d_wlab, wide_batch, d_wgrad, stream)
-                if world > 1:
-                    dist.all_reduce(d_wgrad)
-                wnet.apply_update(d_wgrad, 0.1 / (wide_batch * world), stream)
-
-            wstep()
-            barrier()
-            e0.record(stream)
-            for _ in range(5):
-                wstep()
-            e1.record(stream)
-            barrier()
-            ms = max_over_ranks(e0.elapsed_time(e1)) / 5
-            wide[name] = {"images_per_s": wide_batch * world / (ms * 1e-3), "ms_per_step": ms,
-                          "tflops": 18992896.0 * wide_batch * world / (ms * 1e-3) / 1e12}
-        assert wnet.status() == 0
-        train["train_wide_cfg5"] = {"what": "BASELINE config 5: 56x56 input, 64 maps, batch 1,024 per GPU, "
-                                            "fwd+bwd+update" + (", NCCL all-reduce of 109,856 floats" if world > 1 else ""),
-                                    "conv": wide}
+        train["train_wide_cfg5"] = run_wide_leg()
         barrier()
     except Exception as e:  # pragma: no cover
         train["train_error"] = repr(e)[:300]
@@ -505,6 +518,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--fast-sigmoid", type=int, default=0)
     ap.add_argument("--fw-variant", type=int, default=0)
+    ap.add_argument("--only-wide", type=int, default=0,
+                    help="run only the config-5 leg with conv mode N-1 (1: fp32 SIMT, 2: tf32, 3: 3 x tf32); for ncu")
     ap.add_argument("--only-forward", type=int, default=0,
                     help="run only the forward launches (small, for ncu captures)")
     args = ap.parse_args()

@@ -270,13 +270,13 @@ k_wide_grad_c1(WideDims d, const float* __restrict__ images, const float* __rest
 
 // Sum the per-image partials in image order into the arena-ordered gradient; G[n_params+1] = sum of
 // the per-image error norms; padding zeroed.
-__global__ void k_wide_reduce(WideDims d, long n, const float* __restrict__ part_c, const float* __restrict__ part_s,
-                              const float* __restrict__ err, float* __restrict__ G) {
+__global__ void k_wide_reduce(WideDims d, long n, long rows_c, const float* __restrict__ part_c,
+                              const float* __restrict__ part_s, const float* __restrict__ err, float* __restrict__ G) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int n_c = d.F * 26;
   if (t < n_c) {
     float sum = 0.f;
-    for (long b = 0; b < n; ++b) sum += part_c[(size_t)b * n_c + t];
+    for (long b = 0; b < rows_c; ++b) sum += part_c[(size_t)b * n_c + t];
     const int f = t / 26, k = t % 26;
     if (k < 25) G[d.o_wc + f * 25 + k] = sum; else G[d.o_bc + f] = sum;
   } else if (t < n_c + 17) {
@@ -315,7 +315,8 @@ static int wide_reserve(cnn_wide* w, long n) {
   CNN_CUDA(cudaMalloc(&w->ds, sizeof(float) * (size_t)d.S * n));
   CNN_CUDA(cudaMalloc(&w->delta_f, sizeof(float) * kOut * n));
   CNN_CUDA(cudaMalloc(&w->err, sizeof(float) * n));
-  CNN_CUDA(cudaMalloc(&w->part_c, sizeof(float) * (size_t)d.F * 26 * n));
+  w->part_rows = n > 4096 ? n : 4096;
+  CNN_CUDA(cudaMalloc(&w->part_c, sizeof(float) * (size_t)d.F * 26 * w->part_rows));
   CNN_CUDA(cudaMalloc(&w->part_s, sizeof(float) * 17 * n));
   w->cap = n;
   return CNN_OK;
@@ -450,9 +451,16 @@ int cnn_wide_grad_batch(cnn_wide* w, const float* d_images, const unsigned int* 
   k_wide_bp_c1<<<(unsigned)n, 256, 0, st>>>(d, w->ac, w->ds, w->d_params, w->dc, w->part_s);
   const size_t smem = sizeof(float) * ((size_t)d.H * d.H + 8 * kWideGg * 26);
   CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  k_wide_grad_c1<<<dim3((unsigned)n, (d.F + kWideGg - 1) / kWideGg), 256, smem, st>>>(d, d_images, w->dc, w->part_c);
+  long rows_c = n;
+  if (w->conv_mode > 0 && wide_grad_tc_supported(d)) {
+    int rows = 0;
+    if ((rc = wide_grad_c1_tc(w, d_images, n, &rows, st)) != CNN_OK) return rc;
+    rows_c = rows;
+  } else {
+    k_wide_grad_c1<<<dim3((unsigned)n, (d.F + kWideGg - 1) / kWideGg), 256, smem, st>>>(d, d_images, w->dc, w->part_c);
+  }
   const int n_red = d.F * 26 + 18;
-  k_wide_reduce<<<(n_red + 127) / 128, 128, 0, st>>>(d, n, w->part_c, w->part_s, w->err, d_grad);
+  k_wide_reduce<<<(n_red + 127) / 128, 128, 0, st>>>(d, n, rows_c, w->part_c, w->part_s, w->err, d_grad);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "wide backward launch");
   return CNN_OK;

@@ -31,6 +31,7 @@ struct cnn_wide {
   int flavour = 0;
   int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)
   int* d_status = nullptr;      // bounded-wait status word
+  long part_rows = 0;           // rows of [F][26] that part_c holds
 };
 
 
@@ -38,4 +39,7 @@ namespace cnn {
 bool wide_conv_tc_supported(const WideDims& d);
 // Conv + bias + sigmoid on the tensor cores: writes w->ac for n images.
 int wide_conv_fwd_tc(cnn_wide* w, const float* d_images, long n, cudaStream_t st);
+bool wide_grad_tc_supported(const WideDims& d);
+// Conv weight + bias gradient partials on the tensor cores: fills w->part_c with *rows_out rows of [F][26].
+int wide_grad_c1_tc(cnn_wide* w, const float* d_images, long n, int* rows_out, cudaStream_t st);
 }  // namespace cnn
