@@ -141,21 +141,36 @@ __global__ void k_wide_bp_s1(WideDims d, long n, const float* __restrict__ as, c
   ds[idx] = acc * a * (1.f - a);
 }
 
-// G_wf[k][s] = sum_b delta_f[b][k] as[b][s]   (thread = s, images in index order); also G_bf.
+// G_wf[k][s] = sum_b delta_f[b][k] as[b][s].  The batch is cut into kWideFcSplit contiguous slices
+// (blockIdx.y); each thread owns one s for one slice and writes a partial, and k_wide_grad_fc_sum adds
+// the slices in order, so the result does not depend on scheduling.  Also G_bf.
+constexpr int kWideFcSplit = 16;
+
 __global__ void k_wide_grad_fc(WideDims d, long n, const float* __restrict__ as, const float* __restrict__ delta_f,
-                               float* __restrict__ G) {
+                               float* __restrict__ part_f) {
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
-  if (s < d.S) {
-    float acc[kOut];
+  const long b0 = (n * blockIdx.y) / kWideFcSplit, b1 = (n * (blockIdx.y + 1)) / kWideFcSplit;
+  if (s >= d.S) return;
+  float acc[kOut];
 #pragma unroll
-    for (int k = 0; k < kOut; ++k) acc[k] = 0.f;
-    for (long b = 0; b < n; ++b) {
-      const float v = as[b * d.S + s];
+  for (int k = 0; k < kOut; ++k) acc[k] = 0.f;
+  for (long b = b0; b < b1; ++b) {
+    const float v = as[b * d.S + s];
 #pragma unroll
-      for (int k = 0; k < kOut; ++k) acc[k] = fmaf(delta_f[b * kOut + k], v, acc[k]);
-    }
+    for (int k = 0; k < kOut; ++k) acc[k] = fmaf(delta_f[b * kOut + k], v, acc[k]);
+  }
 #pragma unroll
-    for (int k = 0; k < kOut; ++k) G[d.o_wf + (size_t)k * d.S + s] = acc[k];
+  for (int k = 0; k < kOut; ++k) part_f[((size_t)blockIdx.y * kOut + k) * d.S + s] = acc[k];
+}
+
+__global__ void k_wide_grad_fc_sum(WideDims d, long n, const float* __restrict__ part_f,
+                                   const float* __restrict__ delta_f, float* __restrict__ G) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;   // over kOut * S
+  if (i < (long)kOut * d.S) {
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < kWideFcSplit; ++c) sum += part_f[(size_t)c * kOut * d.S + i];
+    G[d.o_wf + i] = sum;
   }
   if (blockIdx.x == 0 && threadIdx.x < kOut) {
     float acc = 0.f;
@@ -318,6 +333,7 @@ static int wide_reserve(cnn_wide* w, long n) {
   w->part_rows = n > 4096 ? n : 4096;
   CNN_CUDA(cudaMalloc(&w->part_c, sizeof(float) * (size_t)d.F * 26 * w->part_rows));
   CNN_CUDA(cudaMalloc(&w->part_s, sizeof(float) * 17 * n));
+  if (!w->part_f) CNN_CUDA(cudaMalloc(&w->part_f, sizeof(float) * (size_t)kWideFcSplit * kOut * d.S));
   w->cap = n;
   return CNN_OK;
 }
@@ -380,6 +396,7 @@ int cnn_wide_destroy(cnn_wide* w) {
   float* bufs[] = {w->d_params, w->ac, w->dc, w->as, w->ds, w->delta_f, w->err, w->part_c, w->part_s};
   for (float* p : bufs) cudaFree(p);
   cudaFree(w->d_status);
+  cudaFree(w->part_f);
   delete w;
   return CNN_OK;
 }
@@ -447,7 +464,8 @@ int cnn_wide_grad_batch(cnn_wide* w, const float* d_images, const unsigned int* 
   if ((rc = wide_forward_dispatch(w, d_images, d_labels, n, nullptr, nullptr, true, st)) != CNN_OK) return rc;
   const long ns = n * d.S;
   k_wide_bp_s1<<<(unsigned)((ns + 255) / 256), 256, 0, st>>>(d, n, w->as, w->delta_f, w->d_params, w->ds);
-  k_wide_grad_fc<<<(d.S + 127) / 128, 128, 0, st>>>(d, n, w->as, w->delta_f, d_grad);
+  k_wide_grad_fc<<<dim3((d.S + 127) / 128, kWideFcSplit), 128, 0, st>>>(d, n, w->as, w->delta_f, w->part_f);
+  k_wide_grad_fc_sum<<<(unsigned)(((long)kOut * d.S + 255) / 256), 256, 0, st>>>(d, n, w->part_f, w->delta_f, d_grad);
   k_wide_bp_c1<<<(unsigned)n, 256, 0, st>>>(d, w->ac, w->ds, w->d_params, w->dc, w->part_s);
   const size_t smem = sizeof(float) * ((size_t)d.H * d.H + 8 * kWideGg * 26);
   CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -28,6 +28,7 @@ struct cnn_wide {
   long cap = 0;                 // images the workspace holds
   float *ac = nullptr, *dc = nullptr, *as = nullptr, *ds = nullptr, *delta_f = nullptr, *err = nullptr;
   float *part_c = nullptr, *part_s = nullptr;
+  float* part_f = nullptr;      // FC weight-gradient partials of the batch slices
   int flavour = 0;
   int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)
   int* d_status = nullptr;      // bounded-wait status word
