@@ -164,8 +164,10 @@ __device__ __forceinline__ void thread_backward(const TrSmem& sm, const FwdRegs&
 constexpr int kRowStride = kNParamsPadded + 8;
 constexpr int kRowErr = kNParams + 1;  // 2344
 
-template <int FAST>
-__global__ void __launch_bounds__(kTrThreads, 1)
+// MINB = 1: one block per SM, no register cap -- lowest latency, used for small batches.
+// MINB = 2: two blocks per SM at 128 registers -- higher throughput on large batches.
+template <int FAST, int MINB>
+__global__ void __launch_bounds__(kTrThreads, MINB)
 k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ labels, long n,
                 const float* __restrict__ params, float* __restrict__ rows, int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -483,9 +485,15 @@ static int launch_grad_partials(cnn_net* net, const float* d_images, const unsig
   int rc;
 #define CNN_LAUNCH_GRAD(FL)                                                                        \
   do {                                                                                             \
-    if ((rc = set_smem_attr(k_grad_partials<FL>, smem)) != CNN_OK) return rc;                      \
-    k_grad_partials<FL><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params,      \
-                                                        net->d_partials, net->d_status);           \
+    if (grid > sm_count()) {                                                                       \
+      if ((rc = set_smem_attr(k_grad_partials<FL, 2>, smem)) != CNN_OK) return rc;                 \
+      k_grad_partials<FL, 2><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params, \
+                                                             net->d_partials, net->d_status);      \
+    } else {                                                                                       \
+      if ((rc = set_smem_attr(k_grad_partials<FL, 1>, smem)) != CNN_OK) return rc;                 \
+      k_grad_partials<FL, 1><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params, \
+                                                             net->d_partials, net->d_status);      \
+    }                                                                                              \
   } while (0)
   if (net->fast_sigmoid == 1) CNN_LAUNCH_GRAD(1);
   else if (net->fast_sigmoid == 2) CNN_LAUNCH_GRAD(2);
@@ -496,8 +504,10 @@ static int launch_grad_partials(cnn_net* net, const float* d_images, const unsig
   return CNN_OK;
 }
 
+// Small batches: one block per SM (latency).  From 8 images per SM on: two blocks per SM (throughput).
 static int grid_for_batch(long n) {
-  const long cap = sm_count();
+  const long sms = sm_count();
+  const long cap = (n >= 8 * sms) ? 2 * sms : sms;
   return (int)(n < cap ? n : cap);
 }
 
@@ -520,7 +530,7 @@ int cnn_grad_batch(cnn_net* net, const float* d_images, const unsigned int* d_la
   CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
               "cnn_grad_batch: image batch must start on a 16-byte boundary");
   const int grid = grid_for_batch(n);
-  int rc = ensure_train_scratch(net, sm_count());
+  int rc = ensure_train_scratch(net, 2 * sm_count());
   if (rc != CNN_OK) return rc;
   if ((rc = launch_grad_partials(net, d_images, d_labels, n, grid, st)) != CNN_OK) return rc;
   k_reduce_rows<<<(kNParamsPadded + 31) / 32, 128, 0, st>>>(net->d_partials, grid, d_grad, nullptr, 0.f,
@@ -549,7 +559,7 @@ int cnn_train_minibatch(cnn_net* net, const float* d_images, const unsigned int*
               "cnn_train_minibatch: image batch must start on a 16-byte boundary");
   cudaStream_t st = as_stream(stream);
   ++net->params_version;
-  int rc = ensure_train_scratch(net, sm_count());
+  int rc = ensure_train_scratch(net, 2 * sm_count());
   if (rc != CNN_OK) return rc;
   if (d_mean_err) CNN_CUDA(cudaMemsetAsync(d_mean_err, 0, sizeof(float) * (size_t)epochs, st));
   for (int e = 0; e < epochs; ++e) {
@@ -580,7 +590,7 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
               "cnn_train_sgd_persample: image batch must start on a 16-byte boundary");
   cudaStream_t st = as_stream(stream);
   ++net->params_version;
-  int rc = ensure_train_scratch(net, sm_count());
+  int rc = ensure_train_scratch(net, 2 * sm_count());
   if (rc != CNN_OK) return rc;
   // Scratch reuse: d_grad holds the per-epoch means (epochs <= kNParamsPadded) and the epoch count.
   CNN_REQUIRE(epochs <= kNParamsPadded, "cnn_train_sgd_persample: too many epochs");
@@ -668,7 +678,7 @@ int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const u
     float* ptr = nullptr;
     CNN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch));
     CNN_REQUIRE(ptr != nullptr, "cnn_grad_batch_noalloc: no device address for the scratch array");
-    CNN_CUDA(cudaFuncSetAttribute(k_grad_partials<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CNN_CUDA(cudaFuncSetAttribute(k_grad_partials<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)sizeof(TrSmem)));
     scratch_of_device[dev] = ptr;
   }
@@ -682,7 +692,7 @@ int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const u
   // The array keeps what the previous call left: the status word must start at zero (every row that
   // is read below is rewritten in full by its block, padding included).
   CNN_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
-  k_grad_partials<0><<<grid, kTrThreads, sizeof(TrSmem), st>>>(d_images, d_labels, n, d_params, rows, status);
+  k_grad_partials<0, 1><<<grid, kTrThreads, sizeof(TrSmem), st>>>(d_images, d_labels, n, d_params, rows, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch (no-alloc)");
   k_reduce_rows<<<(kNParamsPadded + 31) / 32, 128, 0, st>>>(rows, grid, d_grad, nullptr, 0.f, nullptr, 0.f);
