@@ -219,9 +219,49 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
+_REAL_STDOUT_FD = None
+
+
+def quiet_stdout():
+    """stdout carries exactly one JSON line: everything else that libraries print on fd 1 (NCCL's
+    version banner, for one) is sent to stderr; emit() writes to the saved descriptor."""
+    global _REAL_STDOUT_FD
+    if _REAL_STDOUT_FD is None:
+        sys.stdout.flush()
+        _REAL_STDOUT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT_FD, data)
+
+
+def finish(world: int) -> None:
+    """Leave without hanging in library teardown: synchronise, give the process group ten seconds to
+    shut down cleanly, then exit hard (a CUDA graph that holds NCCL kernels made
+    destroy_process_group block on an 8-GPU run)."""
+    import torch
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if world > 1:
+        import torch.distributed as dist
+        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        t.start()
+        t.join(timeout=10.0)
+    os._exit(0)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
+
+    quiet_stdout()
 
     rank, local_rank, world = dist_env()
     if not torch.cuda.is_available():
@@ -351,20 +391,16 @@ def run_ours(args):
         res = run_wide_leg(modes=((args.only_wide - 1, "conv_mode_%d" % (args.only_wide - 1)),), steps=args.steps)
         sampler.stop()
         if rank == 0:
-            print(json.dumps({"only_wide": True, "train_wide_cfg5": res}), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
+            emit({"only_wide": True, "train_wide_cfg5": res})
+        finish(world)
 
     if args.only_forward:
         # profiling mode: the forward launches only (used under ncu); prints a reduced line
         sampler.stop()
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
-                              "steps": args.steps, "kernel_ms": kernel_ms, "only_forward": True}), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
+            emit({"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
+                  "steps": args.steps, "kernel_ms": kernel_ms, "only_forward": True})
+        finish(world)
 
     # ---- e2e: host buffers through the C ABI ----------------------------------------------------
     h_img = torch.empty((BATCH, 28, 28), dtype=torch.float32).pin_memory()
@@ -446,6 +482,7 @@ def run_ours(args):
             e1.record(stream)
         barrier()
         ms = max_over_ranks(e0.elapsed_time(e1))
+        graph = None   # drop the captured epoch (it holds NCCL kernels) before anything else runs
         train["train_minibatch"] = {
             "images_per_s": n_train / (ms * 1e-3), "global_batch": gb, "steps": steps_t,
             "us_per_step": 1e3 * ms / steps_t, "images": n_train, "launch": graph_note,
@@ -485,9 +522,7 @@ def run_ours(args):
     sampler.stop()
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        finish(world)
 
     cpu = None
     if world == 1:
@@ -524,9 +559,8 @@ def run_ours(args):
     if cpu:
         line["cpu_baseline"] = cpu
     line.update(train)
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    emit(line)
+    finish(world)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_fused_forward launch over 65,536 images,
