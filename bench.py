@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One "step" is one pass of the fused forward kernel over one batch of 65,536 synthetic 28x28 fp32
-images (BASELINE config 2) per GPU.  At N > 1 (launched by torch.distributed.run, one rank per GPU)
+images (benchmark configuration 2) per GPU.  At N > 1 (launched by torch.distributed.run, one rank per GPU)
 every rank runs the same per-GPU batch on its own shard of the synthetic stream with no
 communication (inference shards by image; weak scaling), and the time is the max over ranks.
 
@@ -38,7 +38,7 @@ sys.path.insert(0, ROOT)
 
 import __graft_entry__ as entry  # noqa: E402
 
-BATCH = 65536                 # BASELINE config 2
+BATCH = 65536                 # benchmark configuration 2
 BYTES_PER_IMAGE = 3136 + 40 + 4
 FLOP_PER_IMAGE = 184032
 N_ROTATING = 4                # distinct input buffers (4 x 205.5 MB >> 126 MB L2)
@@ -187,7 +187,7 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(args.steps, 1),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "BASELINE config 2: fused forward over 65,536 synthetic 28x28 fp32 images",
+        "config": {"workload": "benchmark configuration 2: fused forward over 65,536 synthetic 28x28 fp32 images",
                    "sample_images_per_step": n},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": threads, "kind": "port",
                          "sample": "%d images per step (of 65,536), OpenMP over images on all host threads" % n},
@@ -350,7 +350,7 @@ def run_ours(args):
     fp32_peak = n_sm * 128 * 2 * sm_clock_ghz * 1e9
 
     def run_wide_leg(modes=((0, "fp32_simt"), (2, "tf32x3_tcgen05"), (1, "tf32_tcgen05")), steps=5):
-        """BASELINE config 5: widened net (56x56 input, 64 maps), batch 1,024 per GPU, fwd+bwd+update."""
+        """benchmark configuration 5: widened net (56x56 input, 64 maps), batch 1,024 per GPU, fwd+bwd+update."""
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wide_batch = 1024
         wnet = pkg.WideNet(56, 64)
@@ -383,7 +383,7 @@ def run_ours(args):
             wide[name] = {"images_per_s": wide_batch * world / (ms * 1e-3), "ms_per_step": ms,
                           "tflops": 18992896.0 * wide_batch * world / (ms * 1e-3) / 1e12}
         assert wnet.status() == 0
-        return {"what": "BASELINE config 5: 56x56 input, 64 maps, batch 1,024 per GPU, "
+        return {"what": "benchmark configuration 5: 56x56 input, 64 maps, batch 1,024 per GPU, "
                                             "fwd+bwd+update" + (", NCCL all-reduce of 109,856 floats" if world > 1 else ""),
                                     "conv": wide}
 
@@ -486,7 +486,7 @@ def run_ours(args):
         train["train_minibatch"] = {
             "images_per_s": n_train / (ms * 1e-3), "global_batch": gb, "steps": steps_t,
             "us_per_step": 1e3 * ms / steps_t, "images": n_train, "launch": graph_note,
-            "what": "BASELINE config 4, one epoch: fused fwd+bwd gradient kernel, %s, update"
+            "what": "benchmark configuration 4, one epoch: fused fwd+bwd gradient kernel, %s, update"
                     % ("NCCL all-reduce of 2,368 floats" if world > 1 else "single GPU (no collective)"),
             "frac_of_hbm_roofline": (3140 * n_train / (ms * 1e-3) / 1e9) / (peak * world)}
         if rank == 0:
@@ -502,7 +502,7 @@ def run_ours(args):
             ms = e0.elapsed_time(e1) / 5
             train["train_grad_large_batch"] = {"images_per_s": big / (ms * 1e-3), "batch": big,
                                                "frac_of_hbm_roofline": (3140 * big / (ms * 1e-3) / 1e9) / peak}
-            # per-sample SGD, BASELINE config 1: 10,000 images, one epoch, one persistent block
+            # per-sample SGD, benchmark configuration 1: 10,000 images, one epoch, one persistent block
             pnet = pkg.Net(0)
             pnet.set_params(params)
             pnet.train_sgd_persample(d_timg, d_tlab, 500, 1)
@@ -512,7 +512,7 @@ def run_ours(args):
             sec = time.perf_counter() - t0
             train["train_persample"] = {"images_per_s": 10000 / sec, "images": 10000, "epochs": ran,
                                         "mean_err": float(mean_err[0]),
-                                        "what": "BASELINE config 1: per-sample SGD in file order, one persistent block (does not shard)"}
+                                        "what": "benchmark configuration 1: per-sample SGD in file order, one persistent block (does not shard)"}
         barrier()
         train["train_wide_cfg5"] = run_wide_leg()
         barrier()
@@ -536,7 +536,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BASELINE config 2: fused forward, 65,536 synthetic 28x28 fp32 images per GPU per step",
+        "config": {"workload": "benchmark configuration 2: fused forward, 65,536 synthetic 28x28 fp32 images per GPU per step",
                    "images_per_gpu_per_step": BATCH, "global_images_per_step": BATCH * world,
                    "l2": "inputs rotate over %d distinct 205.5 MB buffers (> 126 MB L2)" % N_ROTATING,
                    "sigmoid": SIGMOID_NAMES[args.fast_sigmoid],

@@ -394,7 +394,7 @@ class Net:
 
 
 class WideNet:
-    """The widened variant of the same topology (H x H input, F maps; BASELINE config 5 is
+    """The widened variant of the same topology (H x H input, F maps; benchmark configuration 5 is
     H = 56, F = 64).  Parameters start at zero; set them with ``set_params``."""
 
     def __init__(self, H: int = 56, F: int = 64):

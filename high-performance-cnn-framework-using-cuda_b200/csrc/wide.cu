@@ -1,4 +1,4 @@
-// Widened variant of the same topology (BASELINE config 5): input HxH, F maps of 5x5 (valid) ->
+// Widened variant of the same topology (benchmark configuration 5): input HxH, F maps of 5x5 (valid) ->
 // sigmoid -> ONE shared 4x4/stride-4 filter -> sigmoid -> FC F*P*P -> 10 -> sigmoid, with the
 // reference's update rule generalised as in the oracle: divisors (H-4)^2 for the conv gradient and
 // bias, F*P*P for the subsample bias (layer.cu:369, 389, 312 with 24 -> H-4 and 6*6*6 -> F*P*P).

@@ -1,4 +1,4 @@
-"""The reference's own program as the judge of the drop-in (GPU).
+"""The reference's own program as the arbiter of the drop-in (GPU).
 
 The reference's unmodified main.cu is built twice (oracle/build_dropin.py): against the reference's
 layer.cu and against this repository's compat/layer.cu.  Both binaries, and the fused-kernel driver

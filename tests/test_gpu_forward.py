@@ -125,7 +125,7 @@ def test_forward_against_reference_kernels(cuda, pkg, ob, params0):
 
 
 def test_full_size_property_linearity_in_batch(cuda, pkg, params0):
-    """BASELINE config 2 size (65,536 images): results of a batch do not depend on where an image
+    """benchmark configuration 2 size (65,536 images): results of a batch do not depend on where an image
     sits in it -- the full batch equals the concatenation of two half batches, bit for bit, and the
     device generator fills the same images as the host generator."""
     n = 65536

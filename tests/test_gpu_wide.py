@@ -1,4 +1,4 @@
-"""Widened configuration (BASELINE config 5: 56x56 input, 64 maps) on the GPU against the generalised
+"""Widened configuration (benchmark configuration 5: 56x56 input, 64 maps) on the GPU against the generalised
 oracle; the same kernels at 28x28 / 6 maps against the fused path of the reference net."""
 import numpy as np
 import pytest
@@ -89,7 +89,7 @@ def test_wide_kernels_agree_with_the_fused_reference_net(cuda, pkg, params0):
 
 
 def test_wide_full_batch_runs_and_is_deterministic(cuda, pkg, ob):
-    """BASELINE config 5 size: batch 1,024 of 56x56 images, forward + backward twice, bit-identical."""
+    """benchmark configuration 5 size: batch 1,024 of 56x56 images, forward + backward twice, bit-identical."""
     H, F, n = 56, 64, 1024
     x, labels = wide_inputs(n, H, 3)
     net = pkg.WideNet(H, F)
