@@ -574,7 +574,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--fast-sigmoid", type=int, default=0)
+    ap.add_argument("--fast-sigmoid", type=int, default=2)
     ap.add_argument("--fw-variant", type=int, default=0)
     ap.add_argument("--only-wide", type=int, default=0,
                     help="run only the config-5 leg with conv mode N-1 (1: fp32 SIMT, 2: tf32, 3: 3 x tf32); for ncu")

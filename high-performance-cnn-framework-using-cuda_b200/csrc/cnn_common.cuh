@@ -46,7 +46,7 @@ __device__ __forceinline__ float exp2f_approx(float x) {
 //      for |v| <= 16 (the multiplication by log2e is rounded before the exponential);
 //   2  same two special-function instructions, but with the argument reduced in two FMA steps
 //      (n = round(-v*log2e), r = -v - n*ln2 exactly) and one Newton step on the reciprocal:
-//      about 12 instructions, within a few 1e-7 relative of flavour 0.
+//      about 12 instructions, within a few 1e-7 relative of flavour 0 per evaluation (the default).
 template <int FLAVOR>
 __device__ __forceinline__ float sigmoidf(float v) {
   if constexpr (FLAVOR == 1) {

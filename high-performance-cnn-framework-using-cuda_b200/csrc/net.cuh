@@ -11,7 +11,7 @@ struct cnn_net {
   long params_version = 1;         // bumped whenever the arena may have changed
   float* d_params = nullptr;       // kNParamsPadded floats
   int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out
-  int fast_sigmoid = 0;            // sigmoid flavour 0 / 1 / 2, see sigmoidf in cnn_common.cuh
+  int fast_sigmoid = 2;            // sigmoid flavour 0 / 1 / 2 (default 2), see sigmoidf in cnn_common.cuh
   int fw_variant = 0;              // forward kernel: 0 = scalar kernel, two blocks per SM (default); 1, 2, 3 = experiments
 
   // Training scratch (allocated on first use): per-block partial gradients and the reduced vector.

@@ -29,7 +29,7 @@ struct cnn_wide {
   float *ac = nullptr, *dc = nullptr, *as = nullptr, *ds = nullptr, *delta_f = nullptr, *err = nullptr;
   float *part_c = nullptr, *part_s = nullptr;
   float* part_f = nullptr;      // FC weight-gradient partials of the batch slices
-  int flavour = 0;
+  int flavour = 2;              // sigmoid flavour, as cnn_net
   int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)
   int* d_status = nullptr;      // bounded-wait status word
   long part_rows = 0;           // rows of [F][26] that part_c holds
