@@ -402,33 +402,36 @@ def run_ours(args):
                   "steps": args.steps, "kernel_ms": kernel_ms, "only_forward": True})
         finish(world)
 
-    # ---- e2e: host buffers through the C ABI ----------------------------------------------------
-    h_img = torch.empty((BATCH, 28, 28), dtype=torch.float32).pin_memory()
-    h_img.copy_(bufs[0])
-    h_out = torch.empty((BATCH, 10), dtype=torch.float32).pin_memory()
-    h_arg = torch.empty((BATCH,), dtype=torch.int32).pin_memory()
-    e2e_steps = max(3, min(args.steps, 20))
-    for _ in range(2):
-        net.forward_host(h_img, BATCH, h_out, h_arg)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        net.forward_host(h_img, BATCH, h_out, h_arg)
-    torch.cuda.synchronize()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
-    e2e_value = world * BATCH * e2e_steps / e2e_s
-    barrier()
-    # the same call on uint8 pixels (the IDX storage the reference's loader reads): a quarter of the bytes
-    h_pix = torch.from_numpy(pkg.synth.synth_pixels_u8(1, 4096)).repeat(BATCH // 4096, 1, 1).contiguous().pin_memory()
-    for _ in range(2):
-        net.forward_u8_host(h_pix, BATCH, h_out, h_arg)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        net.forward_u8_host(h_pix, BATCH, h_out, h_arg)
-    torch.cuda.synchronize()
-    e2e_u8_value = world * BATCH * e2e_steps / max_over_ranks(time.perf_counter() - t0)
-    barrier()
+    e2e_value = e2e_u8_value = None
+    e2e_steps = 0
+    if not args.only_train:
+        # ---- e2e: host buffers through the C ABI ----------------------------------------------------
+        h_img = torch.empty((BATCH, 28, 28), dtype=torch.float32).pin_memory()
+        h_img.copy_(bufs[0])
+        h_out = torch.empty((BATCH, 10), dtype=torch.float32).pin_memory()
+        h_arg = torch.empty((BATCH,), dtype=torch.int32).pin_memory()
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(2):
+            net.forward_host(h_img, BATCH, h_out, h_arg)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            net.forward_host(h_img, BATCH, h_out, h_arg)
+        torch.cuda.synchronize()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        e2e_value = world * BATCH * e2e_steps / e2e_s
+        barrier()
+        # the same call on uint8 pixels (the IDX storage the reference's loader reads): a quarter of the bytes
+        h_pix = torch.from_numpy(pkg.synth.synth_pixels_u8(1, 4096)).repeat(BATCH // 4096, 1, 1).contiguous().pin_memory()
+        for _ in range(2):
+            net.forward_u8_host(h_pix, BATCH, h_out, h_arg)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            net.forward_u8_host(h_pix, BATCH, h_out, h_arg)
+        torch.cuda.synchronize()
+        e2e_u8_value = world * BATCH * e2e_steps / max_over_ranks(time.perf_counter() - t0)
+        barrier()
 
     # ---- extra: training legs -------------------------------------------------------------------
     train = {}
@@ -514,12 +517,18 @@ def run_ours(args):
                                         "mean_err": float(mean_err[0]),
                                         "what": "benchmark configuration 1: per-sample SGD in file order, one persistent block (does not shard)"}
         barrier()
-        train["train_wide_cfg5"] = run_wide_leg()
+        if not args.only_train:
+            train["train_wide_cfg5"] = run_wide_leg()
         barrier()
     except Exception as e:  # pragma: no cover
         train["train_error"] = repr(e)[:300]
 
     sampler.stop()
+
+    if args.only_train:
+        if rank == 0:
+            emit({"only_train": True, **train})
+        finish(world)
 
     if rank != 0:
         finish(world)
@@ -576,6 +585,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--fast-sigmoid", type=int, default=2)
     ap.add_argument("--fw-variant", type=int, default=0)
+    ap.add_argument("--only-train", type=int, default=0,
+                    help="run only the training legs of the reference net (for ncu launch lists)")
     ap.add_argument("--only-wide", type=int, default=0,
                     help="run only the config-5 leg with conv mode N-1 (1: fp32 SIMT, 2: tf32, 3: 3 x tf32); for ncu")
     ap.add_argument("--only-forward", type=int, default=0,

@@ -304,24 +304,27 @@ k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ l
   if (tid < kRowStride - kNParams && kNParams + tid != kRowErr) row[kNParams + tid] = 0.f;
 }
 
-// G[i] = sum over rows (fixed order: four interleaved row groups, then group 0..3) and, if params
-// is given, params[i] += scale * G[i].  Element kRowErr carries the error sum; if mean_err is
-// given, *mean_err += err_scale * that sum.  Block: 128 threads = 32 columns x 4 row groups.
-__global__ void __launch_bounds__(128)
+// G[i] = sum over rows (fixed order: eight interleaved row groups, then a fixed tree over the
+// groups) and, if params is given, params[i] += scale * G[i].  Element kRowErr carries the error sum;
+// if mean_err is given, *mean_err += err_scale * that sum.  Block: 256 threads = 32 columns x 8 groups.
+constexpr int kRedGroups = 8;
+
+__global__ void __launch_bounds__(32 * kRedGroups)
 k_reduce_rows(const float* __restrict__ rows, int n_rows, float* __restrict__ G,
               float* __restrict__ params, float scale, float* __restrict__ mean_err, float err_scale) {
-  __shared__ float part[4][33];
+  __shared__ float part[kRedGroups][33];
   const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + lane;
   float acc = 0.f;
   if (col < kRowStride) {
 #pragma unroll 4
-    for (int r = g; r < n_rows; r += 4) acc += rows[(size_t)r * kRowStride + col];
+    for (int r = g; r < n_rows; r += kRedGroups) acc += rows[(size_t)r * kRowStride + col];
   }
   part[g][lane] = acc;
   __syncthreads();
   if (g == 0 && col < kRowStride) {
-    const float total = ((part[0][lane] + part[1][lane]) + part[2][lane]) + part[3][lane];
+    const float total = ((part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane])) +
+                        ((part[4][lane] + part[5][lane]) + (part[6][lane] + part[7][lane]));
     if (G) G[col] = total;
     if (params && col < kNParams) params[col] = fmaf(scale, total, params[col]);
     if (mean_err && col == kRowErr) *mean_err += err_scale * total;
@@ -533,7 +536,7 @@ int cnn_grad_batch(cnn_net* net, const float* d_images, const unsigned int* d_la
   int rc = ensure_train_scratch(net, 2 * sm_count());
   if (rc != CNN_OK) return rc;
   if ((rc = launch_grad_partials(net, d_images, d_labels, n, grid, st)) != CNN_OK) return rc;
-  k_reduce_rows<<<(kNParamsPadded + 31) / 32, 128, 0, st>>>(net->d_partials, grid, d_grad, nullptr, 0.f,
+  k_reduce_rows<<<(kNParamsPadded + 31) / 32, 32 * kRedGroups, 0, st>>>(net->d_partials, grid, d_grad, nullptr, 0.f,
                                                            nullptr, 0.f);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_reduce_rows launch");
@@ -568,7 +571,7 @@ int cnn_train_minibatch(cnn_net* net, const float* d_images, const unsigned int*
       const int grid = grid_for_batch(b);
       if ((rc = launch_grad_partials(net, d_images + first * kImg, d_labels + first, b, grid, st)) != CNN_OK)
         return rc;
-      k_reduce_rows<<<(kNParamsPadded + 31) / 32, 128, 0, st>>>(
+      k_reduce_rows<<<(kNParamsPadded + 31) / 32, 32 * kRedGroups, 0, st>>>(
           net->d_partials, grid, net->d_grad, net->d_params, dt / (float)b,
           d_mean_err ? d_mean_err + e : nullptr, 1.0f / (float)n);
       cudaError_t err = cudaGetLastError();
@@ -695,7 +698,7 @@ int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const u
   k_grad_partials<0, 1><<<grid, kTrThreads, sizeof(TrSmem), st>>>(d_images, d_labels, n, d_params, rows, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch (no-alloc)");
-  k_reduce_rows<<<(kNParamsPadded + 31) / 32, 128, 0, st>>>(rows, grid, d_grad, nullptr, 0.f, nullptr, 0.f);
+  k_reduce_rows<<<(kNParamsPadded + 31) / 32, 32 * kRedGroups, 0, st>>>(rows, grid, d_grad, nullptr, 0.f, nullptr, 0.f);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_reduce_rows launch (no-alloc)");
   return CNN_OK;
