@@ -52,30 +52,33 @@ class Layer {
   static cudaError_t last_error();
 };
 
-// Utility operators
-__device__ float step_function(float v);
-__global__ void apply_step_function(float* input, float* output, const int N);
-__global__ void makeError(float* err, float* output, unsigned int Y, const int N);
-__global__ void apply_grad(float* output, float* grad, const int N);
+// ---- operators -----------------------------------------------------------------------------
+// Launch them exactly as before (any 1-D grid/block works).  "+=" marks operators that accumulate
+// into what their destination already holds, which is why callers clear() / bp_clear() first.
 
-// Forward operators
-__global__ void fp_preact_c1(float input[28][28], float preact[6][24][24], float weight[6][5][5]);
-__global__ void fp_bias_c1(float preact[6][24][24], float bias[6]);
-__global__ void fp_preact_s1(float input[6][24][24], float preact[6][6][6], float weight[1][4][4]);
-__global__ void fp_bias_s1(float preact[6][6][6], float bias[1]);
-__global__ void fp_preact_f(float input[6][6][6], float preact[10], float weight[10][6][6][6]);
-__global__ void fp_bias_f(float preact[10], float bias[10]);
+__device__ float step_function(float v);                                             // 1 / (1 + exp(-v))
+__global__ void apply_step_function(float* z, float* a, const int count);            // a = sigmoid(z)
+__global__ void makeError(float* delta, float* a, unsigned int label, const int count);  // delta = onehot - a
+__global__ void apply_grad(float* params, float* gradient, const int count);         // params += dt * gradient
 
-// Backward operators
-__global__ void bp_weight_f(float d_weight[10][6][6][6], float d_preact[10], float p_output[6][6][6]);
-__global__ void bp_bias_f(float bias[10], float d_preact[10]);
-__global__ void bp_output_s1(float d_output[6][6][6], float n_weight[10][6][6][6], float nd_preact[10]);
-__global__ void bp_preact_s1(float d_preact[6][6][6], float d_output[6][6][6], float preact[6][6][6]);
-__global__ void bp_weight_s1(float d_weight[1][4][4], float d_preact[6][6][6], float p_output[6][24][24]);
-__global__ void bp_bias_s1(float bias[1], float d_preact[6][6][6]);
-__global__ void bp_output_c1(float d_output[6][24][24], float n_weight[1][4][4], float nd_preact[6][6][6]);
-__global__ void bp_preact_c1(float d_preact[6][24][24], float d_output[6][24][24], float preact[6][24][24]);
-__global__ void bp_weight_c1(float d_weight[6][5][5], float d_preact[6][24][24], float p_output[28][28]);
-__global__ void bp_bias_c1(float bias[6], float d_preact[6][24][24]);
+// forward: conv 6 x 5x5 (valid), shared 4x4 / stride-4 subsample, fully connected 216 -> 10
+__global__ void fp_preact_c1(float image[28][28], float z[6][24][24], float filters[6][5][5]);       // z += filters (x) image
+__global__ void fp_bias_c1(float z[6][24][24], float b[6]);                                          // z += b[map]
+__global__ void fp_preact_s1(float a_c1[6][24][24], float z[6][6][6], float filter[1][4][4]);        // z += filter . window
+__global__ void fp_bias_s1(float z[6][6][6], float b[1]);                                            // z += b[0]
+__global__ void fp_preact_f(float a_s1[6][6][6], float z[10], float w[10][6][6][6]);                 // z += w . a_s1
+__global__ void fp_bias_f(float z[10], float b[10]);                                                 // z += b
+
+// backward, in the order the training loop launches them
+__global__ void bp_weight_f(float g_w[10][6][6][6], float delta_f[10], float a_s1[6][6][6]);         // g_w = delta_f (x) a_s1
+__global__ void bp_bias_f(float b[10], float delta_f[10]);                                           // b += dt * delta_f
+__global__ void bp_output_s1(float g_a[6][6][6], float w[10][6][6][6], float delta_f[10]);           // g_a += w^T delta_f
+__global__ void bp_preact_s1(float delta_s[6][6][6], float g_a[6][6][6], float z[6][6][6]);          // delta_s = g_a * sigmoid'(z)
+__global__ void bp_weight_s1(float g_w[1][4][4], float delta_s[6][6][6], float a_c1[6][24][24]);     // g_w += delta_s . windows
+__global__ void bp_bias_s1(float b[1], float delta_s[6][6][6]);                                      // b += dt * mean(delta_s)
+__global__ void bp_output_c1(float g_a[6][24][24], float filter[1][4][4], float delta_s[6][6][6]);   // g_a += filter * delta_s
+__global__ void bp_preact_c1(float delta_c[6][24][24], float g_a[6][24][24], float z[6][24][24]);    // delta_c = g_a * sigmoid'(z)
+__global__ void bp_weight_c1(float g_w[6][5][5], float delta_c[6][24][24], float image[28][28]);     // g_w += delta_c (x) image / 576
+__global__ void bp_bias_c1(float b[6], float delta_c[6][24][24]);                                    // b += dt * mean(delta_c)
 
 #endif  // CNN_B200_COMPAT_LAYER_H
