@@ -36,7 +36,7 @@ struct FwSmem {
 // U8 = false: images are fp32 [n][28][28].  U8 = true: `images` points at uint8 pixels [n][28][28]
 // (the storage of the IDX files the reference reads) and the kernel applies the reference's ingest,
 // float(pixel / 255.0) (mnist.h:145 then main.cu:57-65), through a 256-entry table.
-template <int FAST, int MINB, bool U8>
+template <int FAST, int MINB, bool U8, int UNROLL>
 __global__ void __launch_bounds__(kFwThreads, MINB)
 k_fused_forward(const float* __restrict__ images, long n, const float* __restrict__ params,
                 float* __restrict__ out, int* __restrict__ argmax, int* __restrict__ status) {
@@ -136,7 +136,7 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
 #pragma unroll
     for (int k = 0; k < kOut; ++k) part[k] = 0.f;
 
-#pragma unroll 1
+#pragma unroll UNROLL
     for (int f = 0; f < kF; ++f) {
       float wr[28];
 #pragma unroll
@@ -202,23 +202,25 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
   }
 }
 
-template <int FAST, int MINB, bool U8>
+template <int FAST, int MINB, bool U8, int UNROLL = 1>
 static int launch_variant(cnn_net* net, const void* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
   const long n_tiles = (n + kFwImgs - 1) / kFwImgs;
   const long max_blocks = (long)MINB * sm_count();
   const int grid = (int)(n_tiles < max_blocks ? n_tiles : max_blocks);
   const size_t smem = sizeof(FwSmem);
-  CNN_CUDA(cudaFuncSetAttribute(k_fused_forward<FAST, MINB, U8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  CNN_CUDA(cudaFuncSetAttribute(k_fused_forward<FAST, MINB, U8, UNROLL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)smem));
-  k_fused_forward<FAST, MINB, U8><<<grid, kFwThreads, smem, stream>>>(
+  k_fused_forward<FAST, MINB, U8, UNROLL><<<grid, kFwThreads, smem, stream>>>(
       static_cast<const float*>(d_images), n, net->d_params, d_out, d_argmax, net->d_status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_fused_forward launch");
   return CNN_OK;
 }
 
-// fw_variant: 0 (default) = the scalar kernel of this file, two blocks per SM (register-capped);
+// fw_variant: 0 (default) = the scalar kernel of this file, two blocks per SM (register-capped; with the
+// default sigmoid the loop over the six maps is unrolled by two: 0.447 ms against 0.490 ms per 65,536
+// images, three-fold unrolling spills and is slower);
 // 1 = the same with one block per SM (no cap); 2, 3 = the experiments of fused_forward_x2.cu.
 static int launch_forward(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
@@ -230,7 +232,7 @@ static int launch_forward(cnn_net* net, const float* d_images, long n, float* d_
                    : launch_variant<0, 1, false>(net, d_images, n, d_out, d_argmax, stream);
   }
   return fl == 1 ? launch_variant<1, 2, false>(net, d_images, n, d_out, d_argmax, stream)
-       : fl == 2 ? launch_variant<2, 2, false>(net, d_images, n, d_out, d_argmax, stream)
+       : fl == 2 ? launch_variant<2, 2, false, 2>(net, d_images, n, d_out, d_argmax, stream)
                  : launch_variant<0, 2, false>(net, d_images, n, d_out, d_argmax, stream);
 }
 
@@ -243,7 +245,7 @@ int forward_device_u8(cnn_net* net, const unsigned char* d_pixels, long n, float
                       cudaStream_t stream) {
   const int fl = net->fast_sigmoid;
   return fl == 1 ? launch_variant<1, 2, true>(net, d_pixels, n, d_out, d_argmax, stream)
-       : fl == 2 ? launch_variant<2, 2, true>(net, d_pixels, n, d_out, d_argmax, stream)
+       : fl == 2 ? launch_variant<2, 2, true, 2>(net, d_pixels, n, d_out, d_argmax, stream)
                  : launch_variant<0, 2, true>(net, d_pixels, n, d_out, d_argmax, stream);
 }
 
