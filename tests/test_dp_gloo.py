@@ -67,3 +67,41 @@ def test_two_gloo_ranks_match_single_rank(tmp_path):
     images, labels = pkg.synth.synth_images(3, n)
     pref, _ = ob.train_minibatch(pkg.synth.synth_params(0), images, labels, batch, epochs)
     assert np.max(np.abs(ps - pref)) / np.max(np.abs(pref)) < 1e-6
+
+
+def _infer_worker(rank, world, port, n, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import __graft_entry__ as entry
+    import oracle_binding as ob
+    pkg = entry.load_package()
+    from hpcnn_b200 import parallel
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    lo, hi = parallel.shard_range(n, rank, world)
+    # every rank generates only its own shard of the stream (as bench.py does on the device)
+    images, _ = pkg.synth.synth_images(2, hi - lo, first_index=lo)
+    out, arg = ob.forward_batch(pkg.synth.synth_params(0), images, threads=1)
+    np.savez(os.path.join(out_dir, "shard_%d.npz" % rank), lo=lo, hi=hi, out=out, arg=arg)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_sharded_inference_tiles_the_stream_without_communication(tmp_path):
+    """Inference shards by image: the ranks' contiguous shards, concatenated in rank order, are the
+    single-rank result (no collective on the data path)."""
+    n, world = 103, 2
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_infer_worker, args=(world, port, n, str(tmp_path)), nprocs=world, join=True)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import __graft_entry__ as entry
+    import oracle_binding as ob
+    pkg = entry.load_package()
+    images, _ = pkg.synth.synth_images(2, n)
+    ref_out, ref_arg = ob.forward_batch(pkg.synth.synth_params(0), images, threads=1)
+    parts = [np.load(tmp_path / ("shard_%d.npz" % r)) for r in range(world)]
+    assert parts[0]["lo"] == 0 and parts[-1]["hi"] == n and parts[0]["hi"] == parts[1]["lo"]
+    assert np.array_equal(np.concatenate([p["out"] for p in parts]), ref_out)
+    assert np.array_equal(np.concatenate([p["arg"] for p in parts]), ref_arg)
