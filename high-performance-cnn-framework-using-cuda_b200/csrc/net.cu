@@ -35,7 +35,6 @@ static int ensure_stage(cnn_net* net) {
     CNN_CUDA(cudaMalloc(&net->d_stage_out[s], sizeof(float) * kStageImages * kOut));
     CNN_CUDA(cudaMalloc(&net->d_stage_arg[s], sizeof(int) * kStageImages));
     CNN_CUDA(cudaStreamCreateWithFlags(&net->copy_stream[s], cudaStreamNonBlocking));
-    CNN_CUDA(cudaEventCreateWithFlags(&net->stage_done[s], cudaEventDisableTiming));
   }
   net->stage_images = kStageImages;
   return CNN_OK;
@@ -97,7 +96,6 @@ int cnn_net_destroy(cnn_net* net) {
     cudaFree(net->d_stage_out[s]);
     cudaFree(net->d_stage_arg[s]);
     if (net->copy_stream[s]) cudaStreamDestroy(net->copy_stream[s]);
-    if (net->stage_done[s]) cudaEventDestroy(net->stage_done[s]);
   }
   delete net;
   return CNN_OK;

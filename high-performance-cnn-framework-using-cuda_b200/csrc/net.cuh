@@ -24,7 +24,6 @@ struct cnn_net {
   int* d_stage_arg[2] = {nullptr, nullptr};
   long stage_images = 0;
   cudaStream_t copy_stream[2] = {nullptr, nullptr};
-  cudaEvent_t stage_done[2] = {nullptr, nullptr};
 };
 
 namespace cnn {

@@ -123,3 +123,13 @@ def test_batch_plan(pkg):
         parallel.batch_plan(10, 0)
     with pytest.raises(ValueError):
         parallel.shard_range(10, 3, 3)
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 with nothing but the C library."""
+    import subprocess
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "cnn_b200.h"\nint main(void) { cnn_net* n = 0; (void)n; return CNN_OK; }\n')
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"),
+                        "-fsyntax-only", str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
