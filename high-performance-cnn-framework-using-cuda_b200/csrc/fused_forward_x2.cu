@@ -1,4 +1,6 @@
-// Fused batched forward, packed-FMA version (the default forward kernel).
+// Fused batched forward, experimental variants (selectable with the "fw_variant" option; the default
+// is the scalar kernel of fused_forward.cu, which measured faster): packed-FMA version and a scalar
+// version with constant-bank weights.
 //
 // Same fusion and data movement as fused_forward.cu (bulk-copied image tiles in shared memory, one
 // thread per 4x4 subsample window, nothing but 44 B of results per image written back), with three

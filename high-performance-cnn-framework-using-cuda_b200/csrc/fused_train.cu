@@ -5,7 +5,9 @@
 //    memory (no atomics) and writes one partial row; k_reduce_rows adds the rows in fixed order and
 //    optionally applies the update.  Replaces, per image, forward_pass + makeError + back_pass
 //    (main.cu:67-88, 147-153, 99-119: 17 memsets, 23 launches, one blocking norm).
-//  * k_train_persample -- the reference's learn() loop (main.cu:125-170) as ONE persistent block:
+//  * k_train_persample -- the reference's learn() loop (main.cu:125-170) as ONE persistent block
+//    (the default is the six-CTA cluster kernel of persample_cluster.cu; this one is selected with
+//    the "persample_cluster" option set to 0):
 //    parameters live in shared memory, one SGD step per image in file order, same update
 //    semantics (output delta without sigmoid derivative, every backward product from pre-update
 //    weights, biases and weights stepped by dt), per-epoch mean of ||delta_f||_2, early stop.

@@ -167,8 +167,10 @@ int cnn_forward_batched_u8_host(cnn_net* net, const unsigned char* h_pixels, lon
 int cnn_synth_images(unsigned long long seed, long first_index, long n, float* d_images,
                      unsigned int* d_labels, void* stream);
 
-/* Tuning knobs, by name: "fw_variant" (0 = two blocks per SM with a register cap, 1 = one block per
- * SM), "fast_sigmoid" (as cnn_net_set_fast_sigmoid). */
+/* Tuning knobs, by name: "fw_variant" (0 = default scalar forward kernel, two blocks per SM; 1 = the
+ * same with one block per SM; 2 = packed-FMA experiment; 3 = constant-bank-weights experiment),
+ * "persample_cluster" (1 = default six-CTA cluster kernel for cnn_train_sgd_persample, 0 = single
+ * block), "fast_sigmoid" (as cnn_net_set_fast_sigmoid). */
 int cnn_net_set_option(cnn_net* net, const char* key, int value);
 
 /* ------------------------------------------------------------------------------------------
