@@ -715,6 +715,7 @@ int cnn_copy_to_host(void* h_dst, const void* d_src, size_t bytes) {
 int cnn_copy_to_device(void* d_dst, const void* h_src, size_t bytes) {
   CNN_REQUIRE(d_dst && h_src, "cnn_copy_to_device: NULL argument");
   CNN_CUDA(cudaMemcpy(d_dst, h_src, bytes, cudaMemcpyHostToDevice));
+  CNN_CUDA(cudaStreamSynchronize(cudaStreamLegacy));  // a pageable source may still be in DMA on return
   return CNN_OK;
 }
 

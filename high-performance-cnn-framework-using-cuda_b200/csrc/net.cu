@@ -77,6 +77,8 @@ int cnn_net_create(unsigned int seed, cnn_net** out) {
     for (int j = 0; j < kS; ++j) h[kOffWf + i * kS + j] = draw();
   }
   e = cudaMemcpy(net->d_params, h.data(), sizeof(float) * kNParamsPadded, cudaMemcpyHostToDevice);
+  // the upload and the status memset must have landed before a launch on a non-blocking stream
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     cnn_net_destroy(net);
     return cuda_fail(e, "cnn_net_create: parameter upload");
@@ -103,7 +105,12 @@ int cnn_net_destroy(cnn_net* net) {
 
 int cnn_net_set_params(cnn_net* net, const float* h_params) {
   CNN_REQUIRE(net && h_params, "cnn_net_set_params: NULL argument");
+  // Wait for work in flight that may still read the old values, upload, and wait again: a copy from
+  // pageable memory may return while its DMA is pending, and a launch on a non-blocking stream (the
+  // host pipeline's, or the caller's) is not ordered behind it.
+  CNN_CUDA(cudaDeviceSynchronize());
   CNN_CUDA(cudaMemcpy(net->d_params, h_params, sizeof(float) * kNParams, cudaMemcpyHostToDevice));
+  CNN_CUDA(cudaDeviceSynchronize());
   ++net->params_version;
   return CNN_OK;
 }

@@ -386,6 +386,7 @@ int cnn_wide_create(int H, int F, cnn_wide** out) {
   if (e == cudaSuccess) e = cudaMemset(w->d_params, 0, sizeof(float) * w->d.n_padded);
   if (e == cudaSuccess) e = cudaMalloc(&w->d_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(w->d_status, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();  // memsets are asynchronous to the host
   if (e != cudaSuccess) { delete w; return cuda_fail(e, "cnn_wide_create"); }
   *out = w;
   return CNN_OK;
@@ -403,7 +404,11 @@ int cnn_wide_destroy(cnn_wide* w) {
 
 int cnn_wide_set_params(cnn_wide* w, const float* h_params) {
   CNN_REQUIRE(w && h_params, "cnn_wide_set_params: NULL argument");
+  // same ordering as cnn_net_set_params: nothing in flight reads the old values, and the upload
+  // has landed before a launch on a non-blocking stream
+  CNN_CUDA(cudaDeviceSynchronize());
   CNN_CUDA(cudaMemcpy(w->d_params, h_params, sizeof(float) * w->d.n_params, cudaMemcpyHostToDevice));
+  CNN_CUDA(cudaDeviceSynchronize());
   return CNN_OK;
 }
 

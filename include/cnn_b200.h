@@ -119,7 +119,9 @@ typedef struct cnn_net cnn_net;
  * seed 0 or 1 gives the reference binary's own initial parameters. */
 int cnn_net_create(unsigned int seed, cnn_net** out);
 int cnn_net_destroy(cnn_net* net);
-/* Blocking copies of the 2343-float arena from / to host memory. */
+/* Blocking copies of the 2343-float arena from / to host memory.  cnn_net_set_params waits for all
+ * work on the device before and after its upload, so a launch on any stream (non-blocking ones
+ * included) that follows it sees the new values, and none in flight sees a mixture. */
 int cnn_net_set_params(cnn_net* net, const float* h_params);
 int cnn_net_get_params(cnn_net* net, float* h_params);
 /* Device pointer of the arena (CNN_N_PARAMS floats, padded to 2368), for collectives. */
