@@ -467,6 +467,12 @@ k_train_persample(const float* __restrict__ images, const unsigned* __restrict__
     __syncthreads();
     if (sm.flag[0]) break;
   }
+  // After an early stop up to two prefetched images are still on their way into shared memory:
+  // the block does not exit under them.
+  if (tid == 0) {
+    for (long s2 = step; s2 < total && s2 < step + 2; ++s2)
+      mbar_wait_bounded(&sm.full[s2 & 1], (unsigned)(s2 >> 1) & 1u, status, gave_up);
+  }
 
   // write the parameters back
   for (int i = tid; i < kF * 25; i += kTrThreads) params[kOffWc + i] = sm.wc[i / 25][i % 25];

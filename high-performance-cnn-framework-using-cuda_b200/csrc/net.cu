@@ -141,7 +141,8 @@ int cnn_net_set_option(cnn_net* net, const char* key, int value) {
     return CNN_OK;
   }
   if (std::strcmp(key, "persample_cluster") == 0) {
-    net->ps_cluster = value ? 1 : 0;
+    CNN_REQUIRE(value >= 0 && value <= 2, "cnn_net_set_option: persample_cluster takes 0, 1 or 2");
+    net->ps_cluster = value;
     return CNN_OK;
   }
   if (std::strcmp(key, "fast_sigmoid") == 0) {

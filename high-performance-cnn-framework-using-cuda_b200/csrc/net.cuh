@@ -7,7 +7,8 @@ struct cnn_net {
   int device = 0;
   int id = 0;                      // process-unique, > 0
   int const_slot = 0;              // constant-bank slot of this net (scalar forward variant)
-  int ps_cluster = 1;              // per-sample SGD: 1 = six-CTA cluster kernel (default), 0 = single block
+  int ps_cluster = 2;              // per-sample SGD: six-CTA cluster kernel with one-way stores (2, default) or
+                                   // hardware cluster barriers (1); 0 = single block
   long params_version = 1;         // bumped whenever the arena may have changed
   float* d_params = nullptr;       // kNParamsPadded floats
   int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out

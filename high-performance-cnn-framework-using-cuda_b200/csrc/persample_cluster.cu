@@ -9,8 +9,14 @@
 // parameters (subsample filter and bias, FC bias) are updated identically in every CTA (same
 // values, same order), so they stay bit-identical.
 //
-// Two cluster barriers per sample; the second one is split into arrive / wait around the next
-// sample's convolution, which needs none of the exchanged values, so only the first is exposed.
+// Two exchanges per sample.  With hardware cluster barriers (EXCHANGE = 1) the second barrier is
+// split into arrive / wait around the next sample's convolution, which needs none of the exchanged
+// values, so only the first is exposed.  With one-way stores (EXCHANGE = 2) every value travels as
+// an st.async that counts its bytes on an mbarrier of the receiving CTA; receivers wait on their
+// own mbarrier only, there is no barrier round trip and no release fence, and the buffers alternate
+// with the sample's parity.  The data dependencies alone order the reuse of a buffer: a CTA cannot
+// send the FC partials of sample i+1 before it has every CTA's subsample partials of sample i, which
+// a CTA sends only after it has read the FC partials of sample i (and likewise the other way).
 //
 // Thread (window, row): four x-adjacent conv outputs of one row of a 4x4 subsample window,
 // t = 4 * window + row, 144 live threads in a 160-thread CTA.  Four outputs per thread keep the
@@ -38,14 +44,66 @@ struct ClSmem {
   float wf[kOut][36];           // Wf[k][this map][window]
   float bf[12];
   float fc_part[kClWarps][12];  // per-warp FC partial sums
-  float xfc[kClCtas][12];       // FC partial sums of every CTA (written remotely)
+  float xfc[2][kClCtas][12];    // FC partial sums of every CTA (written remotely), by sample parity
   float c_part[kClWarps][28];   // per-warp conv-filter gradient partials (25) + conv-bias partial
   float s_part[kClWarps][20];   // per-warp subsample-filter gradient partials (16) + bias partial
-  float xws[kClCtas][20];       // subsample gradient partials of every CTA (written remotely)
+  float xws[2][kClCtas][20];    // subsample gradient partials of every CTA (written remotely)
   unsigned label[2];
   unsigned long long full[2];
+  unsigned long long fc_bar[2]; // one-way exchange: bytes of xfc[parity] that have landed
+  unsigned long long ws_bar[2]; // one-way exchange: bytes of xws[parity] that have landed
   int flag[2];
+  long long clock_base;         // phase timing only
 };
+
+constexpr unsigned kFcExchangeBytes = kClCtas * kOut * sizeof(float);   // 240 per receiver and sample
+constexpr unsigned kWsExchangeBytes = kClCtas * 17 * sizeof(float);     // 408
+
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ unsigned cluster_addr(const void* local, unsigned rank) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  return remote;
+}
+// One-way store of a float into another CTA's shared memory; its four bytes are counted on that
+// CTA's mbarrier when they have landed.
+__device__ __forceinline__ void st_async_f32(unsigned remote_addr, float v, unsigned remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(remote_addr),
+               "r"(__float_as_uint(v)), "r"(remote_bar)
+               : "memory");
+}
+// Non-blocking test (test_wait, not try_wait): the exchange waits sit on the critical path of every
+// sample and a suspended try_wait was seen to resume late.
+__device__ __forceinline__ bool mbar_try_wait_cluster(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded like mbar_wait_bounded: about two seconds of SM clocks, then the status word is set and
+// this thread skips every later wait; the other threads of the launch see the word and stop waiting
+// too, so the kernel always ends within seconds.
+__device__ __forceinline__ void mbar_wait_cluster_bounded(unsigned long long* bar, unsigned parity, int* status,
+                                                          bool& gave_up) {
+  if (gave_up) return;
+  if (mbar_try_wait_cluster(bar, parity)) return;
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    // a wait that ran out anywhere ends every other wait of the launch soon after
+    const bool other_gave_up = status && ((++spins & 1023u) == 0) && *reinterpret_cast<volatile int*>(status) != 0;
+    if (other_gave_up || clock64() - t0 > 4000000000LL) {
+      gave_up = true;
+      if (status) atomicExch(status, 1);
+      return;
+    }
+  }
+}
 
 // After the call lane l holds the sum over the warp's lanes of v[l] (unused entries zero-filled).
 __device__ __forceinline__ float warp_reduce_scatter32(float (&v)[32], int lane) {
@@ -62,7 +120,24 @@ __device__ __forceinline__ float warp_reduce_scatter32(float (&v)[32], int lane)
   return v[0];
 }
 
-template <int FLAVOR>
+// Optional phase timing for tuning (off unless the file is compiled with -DCNN_PHASE_CLOCKS): lane 0
+// of every warp of CTA 0 sums, over the samples, the SM clock at each stamp (relative to the clock at
+// kernel start, one counter per SM); means per stamp and warp put all warps on one time axis.
+#ifdef CNN_PHASE_CLOCKS
+__device__ long long g_phase_clocks[kClWarps][16];
+#define CNN_PHASE(i)                                                     \
+  do {                                                                   \
+    if (f == 0 && lane == 0) {                                           \
+      long long now_;                                                    \
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(now_)::"memory");     \
+      ph_[i] += now_ - base_;                                            \
+    }                                                                    \
+  } while (0)
+#else
+#define CNN_PHASE(i) do { } while (0)
+#endif
+
+template <int FLAVOR, int EXCHANGE>
 __global__ void __launch_bounds__(kClThreads, 1)
 k_train_persample_cluster(const float* __restrict__ images, const unsigned* __restrict__ labels, long n,
                           int epochs, float dt, float threshold, float* __restrict__ params,
@@ -78,6 +153,7 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
   const int r = tid & 3;
   const int p = win / 6, q = win % 6;
   const int y = 4 * p + r, x0 = 4 * q;
+  constexpr bool kOneWay = (EXCHANGE == 2);
 
   if (tid < 28) sm.wc[tid] = (tid < 25) ? params[kOffWc + f * 25 + tid] : 0.f;
   if (tid == 0) { sm.bc[0] = params[kOffBc + f]; sm.bs[0] = params[kOffBs]; sm.flag[0] = 0; }
@@ -88,6 +164,10 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
   if (tid == 0) {
     mbar_init(&sm.full[0], 1);
     mbar_init(&sm.full[1], 1);
+    mbar_init(&sm.fc_bar[0], 1);
+    mbar_init(&sm.fc_bar[1], 1);
+    mbar_init(&sm.ws_bar[0], 1);
+    mbar_init(&sm.ws_bar[1], 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -101,35 +181,54 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
   if (tid == 0) {
     if (total > 0) issue(0, 0, labels[0]);
     if (total > 1) issue(1, 1 % n, labels[1 % n]);
+    if (kOneWay && total > 0) {   // the first sample's exchanges are expected before anyone can send
+      mbar_expect_tx(&sm.fc_bar[0], kFcExchangeBytes);
+      mbar_expect_tx(&sm.ws_bar[0], kWsExchangeBytes);
+    }
   }
   cluster.sync();  // every CTA's shared memory is initialised before anyone writes into it remotely
 
+#ifdef CNN_PHASE_CLOCKS
+  long long ph_[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (tid == 0) sm.clock_base = clock64();
+  __syncthreads();
+  const long long base_ = sm.clock_base;
+#endif
   bool gave_up = false;
   bool pending = false;    // a split cluster barrier has been arrived at and not yet waited for
-  float err = 0.f;         // CTA 0, thread 0: running sum of the epoch (a float, like main.cu:130)
-  float delta_keep = 0.f;  // warp 0, lanes 0..9: this sample's delta_f[k], for the deferred bias step
+  float err = 0.f;         // CTA 0, warp 3, lane 0: running sum of the epoch (a float, like main.cu:130)
   int done_epochs = 0;
   long step = 0;
   const float inv_c = 1.0f / (float)(kC * kC);
   const float inv_s = 1.0f / (float)kS;
 
   // Second half of a step: wait for the subsample-gradient partials of all CTAs, apply the update.
+  // `step` is one past the sample whose exchange is pending at both call sites.
   auto finish_update = [&]() {
     if (!pending) return;   // uniform across the cluster
-    cluster.barrier_wait();
-    if (tid < 17) {
+    const int par = (int)((step - 1) & 1);
+    if (kOneWay) {
+      // only the readers wait; the others are held by the block / cluster barrier that follows
+      if (warp == 1) mbar_wait_cluster_bounded(&sm.ws_bar[par], (unsigned)((step - 1) >> 1) & 1u, status, gave_up);
+    } else {
+      cluster.barrier_wait();
+    }
+    // warp 1 has its scheduler to itself (warps 0 and 4 share one and finish the convolution later)
+    if (tid >= 32 && tid < 32 + 17) {
+      const int t = tid - 32;
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < kClCtas; ++c) sum += sm.xws[c][tid];
-      if (tid < 16) sm.ws[tid] = fmaf(dt, sum, sm.ws[tid]);           // apply_grad (s1)
+      for (int c = 0; c < kClCtas; ++c) sum += sm.xws[par][c][t];
+      if (t < 16) sm.ws[t] = fmaf(dt, sum, sm.ws[t]);                 // apply_grad (s1)
       else sm.bs[0] = fmaf(dt, sum, sm.bs[0]);                        // bp_bias_s1
     }
     pending = false;
   };
 
+  if (total > 0) mbar_wait_bounded(&sm.full[0], 0u, status, gave_up);   // the first image
   for (int e = 0; e < epochs; ++e) {
     for (long it = 0; it < n; ++it, ++step) {
-      const int stage = (int)(step & 1);
+      const int stage = (int)(step & 1);   // also the parity of the exchange buffers
       // thread 0 fetches the label of the sample after next now; the load is long done when the
       // stage is re-issued below
       long next_im = 0;
@@ -139,8 +238,10 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
         while (next_im >= n) next_im -= n;
         next_label = labels[next_im];
       }
-      mbar_wait_bounded(&sm.full[stage], (unsigned)(step >> 1) & 1u, status, gave_up);
+      CNN_PHASE(0);   // loop top; the image is there (first sample: waited for before the loop,
+                      // later ones: by warp 4 ahead of the previous sample's last barrier)
       const unsigned label = sm.label[stage];
+      CNN_PHASE(1);
 
       // ---- forward: four conv outputs (y, x0..x0+3) of map f -----------------------------------
       float pt[5][8];
@@ -173,8 +274,11 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
 #pragma unroll
         for (int c = 0; c < 4; ++c) a[c] = sigmoidf<FLAVOR>(acc[c] + b);
       }
+      CNN_PHASE(2);      // patch loads, convolution, four sigmoids
       finish_update();   // previous sample's subsample-filter update (its barrier was split)
+      CNN_PHASE(3);
       __syncthreads();   // that update is visible; every thread has taken its patch and the label
+      CNN_PHASE(4);
       if (tid == 0 && step + 2 < total) issue(stage, next_im, next_label);
 
       // subsample: row r of the window, then the window's four rows
@@ -201,7 +305,9 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
         for (int j = 0; j < 3; ++j)
           if (lane + 4 * j < kOut) sm.fc_part[warp][lane + 4 * j] = pk[j];
       }
+      CNN_PHASE(5);     // subsample, sigmoid, FC partials
       __syncthreads();  // (B1)
+      CNN_PHASE(6);
 
       // ---- CTA partial of the output layer, sent to every CTA --------------------------------
       if (warp == 0) {
@@ -214,32 +320,46 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
         for (int rr = 0; rr < 2; ++rr) {
           const int idx = lane + 32 * rr;         // (destination CTA, k)
           const float v = __shfl_sync(0xffffffffu, zc, idx % kOut);
-          if (idx < kClCtas * kOut) *cluster.map_shared_rank(&sm.xfc[f][idx % kOut], idx / kOut) = v;
+          if (idx < kClCtas * kOut) {
+            float* slot = &sm.xfc[stage][f][idx % kOut];
+            if (kOneWay)
+              st_async_f32(cluster_addr(slot, idx / kOut), v, cluster_addr(&sm.fc_bar[stage], idx / kOut));
+            else
+              *cluster.map_shared_rank(slot, idx / kOut) = v;
+          }
         }
       }
-      cluster.sync();  // (C1) all six partials have landed everywhere
+      // (C1) all six partials have landed everywhere / here
+      CNN_PHASE(7);     // CTA partial and its sends
+      if (kOneWay) {
+        mbar_wait_cluster_bounded(&sm.fc_bar[stage], (unsigned)(step >> 1) & 1u, status, gave_up);
+        CNN_PHASE(8);   // exposed exchange
+        // Expect the next sample's exchanges now: the other barrier pair's previous phases are
+        // complete (waited for one sample ago and earlier in this one), and nobody can send
+        // for the next sample before this CTA's subsample partials of this one, sent further down.
+        if (tid == 0 && step + 1 < total) {
+          mbar_expect_tx(&sm.fc_bar[stage ^ 1], kFcExchangeBytes);
+          mbar_expect_tx(&sm.ws_bar[stage ^ 1], kWsExchangeBytes);
+        }
+      } else {
+        cluster.sync();
+      }
 
       // ---- output layer on lanes 0..9 of every warp --------------------------------------------
       float delta = 0.f;
       if (lane < kOut) {
         float z = 0.f;
 #pragma unroll
-        for (int c = 0; c < kClCtas; ++c) z += sm.xfc[c][lane];
+        for (int c = 0; c < kClCtas; ++c) z += sm.xfc[stage][c][lane];
         z += sm.bf[lane];
         const float o = sigmoidf<FLAVOR>(z);
         delta = ((label == (unsigned)lane) ? 1.0f : 0.0f) - o;   // makeError
-      }
-      if (warp == 0) {
-        delta_keep = delta;
-        float sq = delta * delta;   // zero on lanes >= 10
-#pragma unroll
-        for (int m = 8; m > 0; m >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, m);
-        if (tid == 0) err += sqrtf(sq);
       }
       float d[3];
 #pragma unroll
       for (int j = 0; j < 3; ++j) d[j] = __shfl_sync(0xffffffffu, delta, r + 4 * j);  // lanes 10, 11 hold 0
 
+      CNN_PHASE(9);     // output layer
       // ---- backward --------------------------------------------------------------------------
       float das = wfk[0] * d[0];
       das = fmaf(wfk[1], d[1], das); das = fmaf(wfk[2], d[2], das);
@@ -283,9 +403,20 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
       g[25] = (dc[0] + dc[1]) + (dc[2] + dc[3]);
 #pragma unroll
       for (int t = 26; t < 32; ++t) g[t] = 0.f;
+      CNN_PHASE(10);    // deltas and the thread's gradient terms
       const float mine = warp_reduce_scatter32(g, lane);
       if (lane < 26) sm.c_part[warp][lane] = mine;
+      if (warp == 3) {
+        // warp 3 reaches the barrier well before warps 0 and 4 (which share a scheduler): the
+        // sample's error norm costs nothing here (every warp holds delta_f on its lanes 0..9)
+        float sq = delta * delta;   // zero on lanes >= 10
+#pragma unroll
+        for (int m = 8; m > 0; m >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, m);
+        if (lane == 0) err += sqrtf(sq);
+      }
+      CNN_PHASE(11);    // reduce-scatter
       __syncthreads();  // (B2)
+      CNN_PHASE(12);
 
       if (tid < 26) {
         float sum = 0.f;
@@ -293,25 +424,36 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
         for (int ww = 0; ww < kClWarps; ++ww) sum += sm.c_part[ww][tid];
         if (tid < 25) sm.wc[tid] = fmaf(dt, sum, sm.wc[tid]);          // apply_grad (c1)
         else sm.bc[0] = fmaf(dt, sum, sm.bc[0]);                        // bp_bias_c1
-        if (tid < kOut) sm.bf[tid] = fmaf(dt, delta_keep, sm.bf[tid]);  // bp_bias_f
+      } else if (warp == 3) {
+        if (lane < kOut) sm.bf[lane] = fmaf(dt, delta, sm.bf[lane]);    // bp_bias_f
+      } else if (warp == 4) {
+        // the next sample's image: one idle warp observes its arrival, the barrier below hands
+        // that on to the others, and nobody waits for it at the top of the loop
+        if (step + 1 < total)
+          mbar_wait_bounded(&sm.full[stage ^ 1], (unsigned)((step + 1) >> 1) & 1u, status, gave_up);
       } else if (tid >= 32 && tid < 32 + 17) {
         const int t = tid - 32;
         float sum = 0.f;
 #pragma unroll
         for (int ww = 0; ww < kClWarps; ++ww) sum += sm.s_part[ww][t];
 #pragma unroll
-        for (int c = 0; c < kClCtas; ++c) *cluster.map_shared_rank(&sm.xws[f][t], c) = sum;
+        for (int c = 0; c < kClCtas; ++c) {
+          float* slot = &sm.xws[stage][f][t];
+          if (kOneWay) st_async_f32(cluster_addr(slot, c), sum, cluster_addr(&sm.ws_bar[stage], c));
+          else *cluster.map_shared_rank(slot, c) = sum;
+        }
       }
-      // (C2, split) arrive now; the wait sits after the next sample's convolution.  The arrive also
-      // orders this CTA's local updates of wc / bc / bf before its own next convolution only through
-      // the __syncthreads below.
+      // (C2, split) arrive now; the wait sits after the next sample's convolution.  This CTA's own
+      // updates of wc / bc / bf are ordered before its next convolution by the __syncthreads.
+      CNN_PHASE(13);    // conv-filter update / subsample partial sends
       __syncthreads();
-      cluster.barrier_arrive();
+      CNN_PHASE(14);
+      if (!kOneWay) cluster.barrier_arrive();
       pending = true;
     }
     // epoch end, main.cu:159-166: every CTA must take the same branch
     finish_update();
-    if (f == 0 && tid == 0) {
+    if (f == 0 && tid == 96) {
       const float m = err / (float)n;
       if (mean_err) mean_err[e] = m;
       err = 0.f;
@@ -325,6 +467,12 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
     if (stop) break;
   }
 
+  // After an early stop up to two prefetched images are still on their way into this CTA's shared
+  // memory: the CTA does not exit under them.
+  if (tid == 0) {
+    for (long s2 = step; s2 < total && s2 < step + 2; ++s2)
+      mbar_wait_bounded(&sm.full[s2 & 1], (unsigned)(s2 >> 1) & 1u, status, gave_up);
+  }
   __syncthreads();
   if (tid < 25) params[kOffWc + f * 25 + tid] = sm.wc[tid];
   if (tid == 0) params[kOffBc + f] = sm.bc[0];
@@ -336,13 +484,17 @@ k_train_persample_cluster(const float* __restrict__ images, const unsigned* __re
     if (tid < kOut) params[kOffBf + tid] = sm.bf[tid];
     if (tid == 0 && epochs_run) *epochs_run = done_epochs;
   }
+#ifdef CNN_PHASE_CLOCKS
+  if (f == 0 && lane == 0)
+    for (int i = 0; i < 16; ++i) g_phase_clocks[warp][i] = ph_[i];
+#endif
 }
 
-template <int FLAVOR>
+template <int FLAVOR, int EXCHANGE>
 static int launch_cluster_flavor(const float* d_images, const unsigned* d_labels, long n, int epochs,
                                  float dt, float threshold, float* d_params, float* d_mean, int* d_ran,
                                  int* d_status, cudaStream_t st) {
-  auto kernel = k_train_persample_cluster<FLAVOR>;
+  auto kernel = k_train_persample_cluster<FLAVOR, EXCHANGE>;
   CNN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClSmem)));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kClCtas, 1, 1);
@@ -363,11 +515,28 @@ static int launch_cluster_flavor(const float* d_images, const unsigned* d_labels
 
 int launch_persample_cluster(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
                              float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st) {
-  switch (net->fast_sigmoid) {
-    case 1: return launch_cluster_flavor<1>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
-    case 2: return launch_cluster_flavor<2>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
-    default: return launch_cluster_flavor<0>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
+#define CNN_CLUSTER_CASE(FL, EX)                                                                              \
+  return launch_cluster_flavor<FL, EX>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, \
+                                       d_ran, net->d_status, st)
+  if (net->ps_cluster == 2) {
+    switch (net->fast_sigmoid) {
+      case 1: CNN_CLUSTER_CASE(1, 2);
+      case 2: CNN_CLUSTER_CASE(2, 2);
+      default: CNN_CLUSTER_CASE(0, 2);
+    }
   }
+  switch (net->fast_sigmoid) {
+    case 1: CNN_CLUSTER_CASE(1, 1);
+    case 2: CNN_CLUSTER_CASE(2, 1);
+    default: CNN_CLUSTER_CASE(0, 1);
+  }
+#undef CNN_CLUSTER_CASE
 }
 
 }  // namespace cnn
+
+#ifdef CNN_PHASE_CLOCKS
+extern "C" int cnn_debug_phase_clocks(long long* out32 /* [5][16] */) {
+  return cudaMemcpyFromSymbol(out32, cnn::g_phase_clocks, sizeof(cnn::g_phase_clocks)) == cudaSuccess ? 0 : 2;
+}
+#endif

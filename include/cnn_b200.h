@@ -171,8 +171,10 @@ int cnn_synth_images(unsigned long long seed, long first_index, long n, float* d
 
 /* Tuning knobs, by name: "fw_variant" (0 = default scalar forward kernel, two blocks per SM; 1 = the
  * same with one block per SM; 2 = packed-FMA experiment; 3 = constant-bank-weights experiment),
- * "persample_cluster" (1 = default six-CTA cluster kernel for cnn_train_sgd_persample, 0 = single
- * block), "fast_sigmoid" (as cnn_net_set_fast_sigmoid). */
+ * "persample_cluster" (kernel of cnn_train_sgd_persample: 2 = default, a cluster of six CTAs that
+ * exchange partial sums by one-way stores counted on mbarriers; 1 = the same cluster with hardware
+ * cluster barriers, bit-identical results; 0 = single block), "fast_sigmoid" (as
+ * cnn_net_set_fast_sigmoid). */
 int cnn_net_set_option(cnn_net* net, const char* key, int value);
 
 /* ------------------------------------------------------------------------------------------

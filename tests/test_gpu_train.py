@@ -152,6 +152,29 @@ def test_persample_early_stop_and_determinism(cuda, pkg, params0):
     assert ran == 0
 
 
+@pytest.mark.parametrize("fast", [0, 1, 2])
+def test_persample_exchange_modes_are_bit_identical(cuda, pkg, params0, fast):
+    """The cluster kernel's two exchange mechanisms (hardware cluster barriers; one-way stores counted
+    on mbarriers) add the same values in the same order: parameters and epoch errors agree bit for
+    bit over 3 epochs of 700 samples, and so does an early stop."""
+    n = 700
+    images, labels = pkg.synth.synth_images(41, n)
+    d_img, d_lab = to_dev(cuda, images, labels)
+    got = {}
+    for mode in (1, 2):
+        net = pkg.Net(0)
+        net.set_params(params0)
+        net.set_fast_sigmoid(fast)
+        net.set_option("persample_cluster", mode)
+        ran, mean_err = net.train_sgd_persample(d_img, d_lab, n, 3)
+        assert ran == 3 and net.status() == 0
+        ran1, me1 = net.train_sgd_persample(d_img, d_lab, 1, 4, threshold=100.0)   # stops after one epoch
+        assert ran1 == 1
+        got[mode] = (net.get_params(), np.asarray(mean_err), np.asarray(me1))
+    for a, b in zip(got[1], got[2]):
+        assert np.array_equal(a, b)
+
+
 @pytest.mark.parametrize("n,batch", [(600, 256), (256, 256), (100, 7), (5, 1)])
 def test_minibatch_training_matches_oracle(cuda, pkg, ob, params0, n, batch):
     images, labels = pkg.synth.synth_images(37, n)
