@@ -505,7 +505,7 @@ def run_ours(args):
             ms = e0.elapsed_time(e1) / 5
             train["train_grad_large_batch"] = {"images_per_s": big / (ms * 1e-3), "batch": big,
                                                "frac_of_hbm_roofline": (3140 * big / (ms * 1e-3) / 1e9) / peak}
-            # per-sample SGD, benchmark configuration 1: 10,000 images, one epoch, one persistent block
+            # per-sample SGD, benchmark configuration 1: 10,000 images, one epoch, one persistent six-CTA cluster
             pnet = pkg.Net(0)
             pnet.set_params(params)
             pnet.train_sgd_persample(d_timg, d_tlab, 500, 1)
@@ -515,7 +515,7 @@ def run_ours(args):
             sec = time.perf_counter() - t0
             train["train_persample"] = {"images_per_s": 10000 / sec, "images": 10000, "epochs": ran,
                                         "mean_err": float(mean_err[0]),
-                                        "what": "benchmark configuration 1: per-sample SGD in file order, one persistent block (does not shard)"}
+                                        "what": "benchmark configuration 1: per-sample SGD in file order, one persistent cluster of six CTAs (does not shard)"}
         barrier()
         if not args.only_train:
             train["train_wide_cfg5"] = run_wide_leg()

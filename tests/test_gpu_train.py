@@ -175,6 +175,24 @@ def test_persample_exchange_modes_are_bit_identical(cuda, pkg, params0, fast):
         assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_persample_kernels_single_step_matches_oracle(cuda, pkg, ob, params0, mode):
+    """Three SGD steps from identical state with the reference sigmoid, for each per-sample kernel
+    (single block, cluster with hardware barriers, cluster with one-way stores): 1e-5 of the largest
+    parameter, and the epoch's mean error norm."""
+    images, labels = pkg.synth.synth_images(42, 3)
+    d_img, d_lab = to_dev(cuda, images, labels)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.set_fast_sigmoid(0)
+    net.set_option("persample_cluster", mode)
+    ran, mean_err = net.train_sgd_persample(d_img, d_lab, 3, 1)
+    p_or, m_or, _ = ob.train_persample(params0, images, labels, 1)
+    assert ran == 1 and net.status() == 0
+    assert scaled_err(net.get_params(), p_or) < 1e-5
+    assert np.allclose(mean_err, m_or, rtol=1e-5)
+
+
 @pytest.mark.parametrize("n,batch", [(600, 256), (256, 256), (100, 7), (5, 1)])
 def test_minibatch_training_matches_oracle(cuda, pkg, ob, params0, n, batch):
     images, labels = pkg.synth.synth_images(37, n)
