@@ -516,6 +516,18 @@ def run_ours(args):
             train["train_persample"] = {"images_per_s": 10000 / sec, "images": 10000, "epochs": ran,
                                         "mean_err": float(mean_err[0]),
                                         "what": "benchmark configuration 1: per-sample SGD in file order, one persistent cluster of six CTAs (does not shard)"}
+            # the same through the option that selects the variant with eight outputs per thread and a
+            # service warp (cnn_net_set_option "persample_cluster" = 3)
+            pnet.set_option("persample_cluster", 3)
+            pnet.set_params(params)
+            pnet.train_sgd_persample(d_timg, d_tlab, 500, 1)
+            pnet.set_params(params)
+            t0 = time.perf_counter()
+            ran, mean_err = pnet.train_sgd_persample(d_timg, d_tlab, 10000, 1)
+            sec = time.perf_counter() - t0
+            train["train_persample_option3"] = {"images_per_s": 10000 / sec, "images": 10000, "epochs": ran,
+                                                "mean_err": float(mean_err[0]),
+                                                "what": "the same with option persample_cluster = 3 (eight conv outputs per thread, service warp)"}
         barrier()
         if not args.only_train:
             train["train_wide_cfg5"] = run_wide_leg()

@@ -608,7 +608,10 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   float* d_mean = net->d_grad;
   int* d_ran = reinterpret_cast<int*>(net->d_grad + kNParamsPadded);
   const size_t smem = sizeof(TrSmem);
-  if (net->ps_cluster) {
+  if (net->ps_cluster == 3) {
+    if ((rc = launch_persample_cluster8(net, d_images, d_labels, n, epochs, dt, threshold, d_mean, d_ran, st)) != CNN_OK)
+      return rc;
+  } else if (net->ps_cluster) {
     if ((rc = launch_persample_cluster(net, d_images, d_labels, n, epochs, dt, threshold, d_mean, d_ran, st)) != CNN_OK)
       return rc;
   } else {

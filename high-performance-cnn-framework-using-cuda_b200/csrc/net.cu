@@ -141,7 +141,7 @@ int cnn_net_set_option(cnn_net* net, const char* key, int value) {
     return CNN_OK;
   }
   if (std::strcmp(key, "persample_cluster") == 0) {
-    CNN_REQUIRE(value >= 0 && value <= 2, "cnn_net_set_option: persample_cluster takes 0, 1 or 2");
+    CNN_REQUIRE(value >= 0 && value <= 3, "cnn_net_set_option: persample_cluster takes 0 to 3");
     net->ps_cluster = value;
     return CNN_OK;
   }

@@ -8,7 +8,8 @@ struct cnn_net {
   int id = 0;                      // process-unique, > 0
   int const_slot = 0;              // constant-bank slot of this net (scalar forward variant)
   int ps_cluster = 2;              // per-sample SGD: six-CTA cluster kernel with one-way stores (2, default) or
-                                   // hardware cluster barriers (1); 0 = single block
+                                   // hardware cluster barriers (1); 3 = eight outputs per thread and a
+                                   // service warp; 0 = single block
   long params_version = 1;         // bumped whenever the arena may have changed
   float* d_params = nullptr;       // kNParamsPadded floats
   int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out
@@ -83,6 +84,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 }
 
 int ensure_train_scratch(cnn_net* net, int rows);
+int launch_persample_cluster8(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
+                              float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st);
 int launch_persample_cluster(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
                              float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st);
 int launch_forward_x2(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,

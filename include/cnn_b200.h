@@ -173,8 +173,9 @@ int cnn_synth_images(unsigned long long seed, long first_index, long n, float* d
  * same with one block per SM; 2 = packed-FMA experiment; 3 = constant-bank-weights experiment),
  * "persample_cluster" (kernel of cnn_train_sgd_persample: 2 = default, a cluster of six CTAs that
  * exchange partial sums by one-way stores counted on mbarriers; 1 = the same cluster with hardware
- * cluster barriers, bit-identical results; 0 = single block), "fast_sigmoid" (as
- * cnn_net_set_fast_sigmoid). */
+ * cluster barriers, bit-identical results; 3 = the one-way cluster with eight conv outputs per
+ * thread and a service warp, the fastest measured, sums in another order so results agree with the
+ * default to rounding; 0 = single block), "fast_sigmoid" (as cnn_net_set_fast_sigmoid). */
 int cnn_net_set_option(cnn_net* net, const char* key, int value);
 
 /* ------------------------------------------------------------------------------------------

@@ -175,11 +175,12 @@ def test_persample_exchange_modes_are_bit_identical(cuda, pkg, params0, fast):
         assert np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
 def test_persample_kernels_single_step_matches_oracle(cuda, pkg, ob, params0, mode):
     """Three SGD steps from identical state with the reference sigmoid, for each per-sample kernel
-    (single block, cluster with hardware barriers, cluster with one-way stores): 1e-5 of the largest
-    parameter, and the epoch's mean error norm."""
+    (single block; cluster with hardware barriers; cluster with one-way stores; cluster with eight
+    outputs per thread and a service warp): 1e-5 of the largest parameter, and the epoch's mean
+    error norm."""
     images, labels = pkg.synth.synth_images(42, 3)
     d_img, d_lab = to_dev(cuda, images, labels)
     net = pkg.Net(0)
@@ -191,6 +192,36 @@ def test_persample_kernels_single_step_matches_oracle(cuda, pkg, ob, params0, mo
     assert ran == 1 and net.status() == 0
     assert scaled_err(net.get_params(), p_or) < 1e-5
     assert np.allclose(mean_err, m_or, rtol=1e-5)
+
+
+@pytest.mark.parametrize("fast", [0, 2])
+def test_persample_eight_output_variant(cuda, pkg, ob, params0, fast):
+    """The cluster kernel with eight outputs per thread adds the same terms in another order: over 3
+    epochs of 700 samples it stays within the trajectory bar of the oracle and of the default kernel,
+    stops early like it, and repeats itself bit for bit."""
+    n = 700
+    images, labels = pkg.synth.synth_images(43, n)
+    d_img, d_lab = to_dev(cuda, images, labels)
+    got = {}
+    for mode in (2, 3, 3):
+        net = pkg.Net(0)
+        net.set_params(params0)
+        net.set_fast_sigmoid(fast)
+        net.set_option("persample_cluster", mode)
+        ran, mean_err = net.train_sgd_persample(d_img, d_lab, n, 3)
+        assert ran == 3 and net.status() == 0
+        p = net.get_params()
+        ran1, _ = net.train_sgd_persample(d_img, d_lab, 1, 4, threshold=100.0)   # stops after one epoch
+        assert ran1 == 1 and net.status() == 0
+        if mode in got:
+            assert np.array_equal(got[mode][0], p) and np.array_equal(got[mode][1], mean_err)
+        got[mode] = (p, np.asarray(mean_err))
+    assert scaled_err(got[3][0], got[2][0]) < 1e-3
+    assert np.allclose(got[3][1], got[2][1], rtol=1e-4)
+    p_or, m_or, ran_or = ob.train_persample(params0, images, labels, 3)
+    assert ran_or == 3
+    assert scaled_err(got[3][0], p_or) < 1e-3
+    assert np.allclose(got[3][1], m_or, rtol=1e-4)
 
 
 @pytest.mark.parametrize("n,batch", [(600, 256), (256, 256), (100, 7), (5, 1)])
