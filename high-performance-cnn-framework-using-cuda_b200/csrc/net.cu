@@ -1,4 +1,5 @@
 // Fused-network handle: parameter arena, status word, and the host-buffer forward pipeline.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -50,8 +51,8 @@ int cnn_net_create(unsigned int seed, cnn_net** out) {
   *out = nullptr;
   cnn_net* net = new (std::nothrow) cnn_net();
   CNN_REQUIRE(net != nullptr, "cnn_net_create: out of host memory");
-  static int next_id = 0;
-  net->id = ++next_id;
+  static std::atomic<int> next_id{0};   // nets may be created from several host threads
+  net->id = next_id.fetch_add(1) + 1;
   net->const_slot = net->id % 8;
   cudaError_t e = cudaGetDevice(&net->device);
   if (e == cudaSuccess) e = cudaMalloc(&net->d_params, sizeof(float) * kNParamsPadded);
