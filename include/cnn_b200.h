@@ -116,7 +116,9 @@ typedef struct cnn_net cnn_net;
 
 /* Creates the net on the current CUDA device.  Parameters are drawn like the reference's static
  * Layer objects would draw them after srand(seed) (c1, s1, f in that order; main.cu:17-20), so
- * seed 0 or 1 gives the reference binary's own initial parameters. */
+ * seed 0 or 1 gives the reference binary's own initial parameters.  The draw goes through the C
+ * library's srand / rand, like the reference's: it reseeds the process-wide generator and must not
+ * run concurrently with other users of rand(). */
 int cnn_net_create(unsigned int seed, cnn_net** out);
 int cnn_net_destroy(cnn_net* net);
 /* Blocking copies of the 2343-float arena from / to host memory.  cnn_net_set_params waits for all
