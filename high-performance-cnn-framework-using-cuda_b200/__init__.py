@@ -20,7 +20,7 @@ from typing import Optional
 
 import numpy as np
 
-from . import synth  # noqa: F401  (re-exported)
+from . import checkpoint, synth  # noqa: F401  (re-exported)
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libcnn_b200.so")
@@ -115,6 +115,11 @@ _PROTOTYPES = {
     "cnn_copy_to_device": (C.c_int, [_P, _P, C.c_size_t]),
     "cnn_grad_batch": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
     "cnn_grad_batch_noalloc": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
+    "cnn_grad_batch_noalloc_status": (C.c_int, [_P]),
+    "cnn_net_save": (C.c_int, [_P, C.c_char_p]),
+    "cnn_net_load": (C.c_int, [_P, C.c_char_p]),
+    "cnn_wide_save": (C.c_int, [_P, C.c_char_p]),
+    "cnn_wide_load": (C.c_int, [_P, C.c_char_p]),
     "cnn_apply_update": (C.c_int, [_P, _P, C.c_float, _P]),
     "cnn_train_minibatch": (C.c_int, [_P, _P, _P, C.c_long, C.c_int, C.c_int, C.c_float, _P, _P]),
     "cnn_train_sgd_persample": (C.c_int, [_P, _P, _P, C.c_long, C.c_int, C.c_float, C.c_float, _P, C.POINTER(C.c_int), _P]),
@@ -319,10 +324,17 @@ class Net:
         return int(p.value)
 
     def set_fast_sigmoid(self, flavour) -> None:
-        """Sigmoid flavour of the fused kernels: 0/False = the reference expression, 1/True =
-        ex2/rcp approximations (about 1e-6 relative), 2 = reduced-argument ex2 + refined reciprocal
-        (a few 1e-7 relative)."""
+        """Sigmoid flavour of the fused kernels: 0/False = the reference expression, anything else =
+        reduced-argument ex2 + refined reciprocal (a few 1e-7 relative; the default)."""
         _check(load_library().cnn_net_set_fast_sigmoid(self._h, int(flavour)))
+
+    def save(self, path: str) -> None:
+        """Write the parameter arena as a checkpoint file (format: ``checkpoint.py``)."""
+        _check(load_library().cnn_net_save(self._h, os.fsencode(path)))
+
+    def load(self, path: str) -> None:
+        """Read a checkpoint written by ``save`` (or ``checkpoint.write_checkpoint``) into the arena."""
+        _check(load_library().cnn_net_load(self._h, os.fsencode(path)))
 
     def set_option(self, key: str, value: int) -> None:
         _check(load_library().cnn_net_set_option(self._h, key.encode(), int(value)))
@@ -420,6 +432,12 @@ class WideNet:
     def set_option(self, key: str, value: int) -> None:
         _check(load_library().cnn_wide_set_option(self._h, key.encode(), int(value)))
 
+    def save(self, path: str) -> None:
+        _check(load_library().cnn_wide_save(self._h, os.fsencode(path)))
+
+    def load(self, path: str) -> None:
+        _check(load_library().cnn_wide_load(self._h, os.fsencode(path)))
+
     def status(self) -> int:
         s = C.c_int(0)
         _check(load_library().cnn_wide_status(self._h, C.byref(s)))
@@ -455,6 +473,12 @@ def grad_batch_noalloc(d_params, d_images, d_labels, n: int, d_grad, stream=None
     most 65,536 images per call; calls that can overlap on the GPU share that array and race."""
     _check(load_library().cnn_grad_batch_noalloc(_ptr(d_params), _ptr(d_images), _ptr(d_labels), int(n),
                                                  _ptr(d_grad), _stream(stream)))
+
+
+def grad_batch_noalloc_status(stream=None) -> None:
+    """Waits for ``stream`` and raises ``CnnError`` (code -3) if a ``grad_batch_noalloc`` call on the
+    current device gave up a bounded wait since the last query.  Allocates nothing."""
+    _check(load_library().cnn_grad_batch_noalloc_status(_stream(stream)))
 
 
 def synth_images_device(seed: int, first_index: int, n: int, d_images, d_labels=None, stream=None) -> None:

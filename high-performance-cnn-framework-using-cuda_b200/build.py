@@ -16,7 +16,8 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libcnn_b200.so")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 
-SOURCES = ["layer_abi.cu", "net.cu", "fused_forward.cu", "fused_forward_x2.cu", "fused_train.cu", "persample_cluster.cu", "persample_cluster8.cu", "wide.cu", "wide_tc.cu", "synth.cu"]
+SOURCES = ["layer_abi.cu", "net.cu", "checkpoint.cu", "fused_forward.cu", "fused_train.cu",
+           "persample_cluster8.cu", "wide.cu", "wide_tc.cu", "synth.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

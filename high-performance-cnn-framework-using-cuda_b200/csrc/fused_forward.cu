@@ -202,51 +202,35 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
   }
 }
 
-template <int FAST, int MINB, bool U8, int UNROLL = 1>
+template <int FAST, bool U8, int UNROLL>
 static int launch_variant(cnn_net* net, const void* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
+  constexpr int kMinBlocks = 2;   // two 9-warp blocks per SM: 96 registers per thread
   const long n_tiles = (n + kFwImgs - 1) / kFwImgs;
-  const long max_blocks = (long)MINB * sm_count();
+  const long max_blocks = (long)kMinBlocks * sm_count();
   const int grid = (int)(n_tiles < max_blocks ? n_tiles : max_blocks);
   const size_t smem = sizeof(FwSmem);
-  CNN_CUDA(cudaFuncSetAttribute(k_fused_forward<FAST, MINB, U8, UNROLL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)smem));
-  k_fused_forward<FAST, MINB, U8, UNROLL><<<grid, kFwThreads, smem, stream>>>(
+  CNN_CUDA(cudaFuncSetAttribute(k_fused_forward<FAST, kMinBlocks, U8, UNROLL>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_fused_forward<FAST, kMinBlocks, U8, UNROLL><<<grid, kFwThreads, smem, stream>>>(
       static_cast<const float*>(d_images), n, net->d_params, d_out, d_argmax, net->d_status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_fused_forward launch");
   return CNN_OK;
 }
 
-// fw_variant: 0 (default) = the scalar kernel of this file, two blocks per SM (register-capped; with the
-// default sigmoid the loop over the six maps is unrolled by two: 0.447 ms against 0.490 ms per 65,536
-// images, three-fold unrolling spills and is slower);
-// 1 = the same with one block per SM (no cap); 2, 3 = the experiments of fused_forward_x2.cu.
-static int launch_forward(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
-                          cudaStream_t stream) {
-  if (net->fw_variant >= 2) return launch_forward_x2(net, d_images, n, d_out, d_argmax, stream);
-  const int fl = net->fast_sigmoid;
-  if (net->fw_variant == 1) {
-    return fl == 1 ? launch_variant<1, 1, false>(net, d_images, n, d_out, d_argmax, stream)
-         : fl == 2 ? launch_variant<2, 1, false>(net, d_images, n, d_out, d_argmax, stream)
-                   : launch_variant<0, 1, false>(net, d_images, n, d_out, d_argmax, stream);
-  }
-  return fl == 1 ? launch_variant<1, 2, false>(net, d_images, n, d_out, d_argmax, stream)
-       : fl == 2 ? launch_variant<2, 2, false, 2>(net, d_images, n, d_out, d_argmax, stream)
-                 : launch_variant<0, 2, false>(net, d_images, n, d_out, d_argmax, stream);
-}
-
+// With the default sigmoid the loop over the six maps is unrolled by two (more independent sigmoid
+// chains in flight at the same 96 registers); three-fold unrolling spills.
 int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                    cudaStream_t stream) {
-  return launch_forward(net, d_images, n, d_out, d_argmax, stream);
+  return net->fast_sigmoid ? launch_variant<2, false, 2>(net, d_images, n, d_out, d_argmax, stream)
+                           : launch_variant<0, false, 1>(net, d_images, n, d_out, d_argmax, stream);
 }
 
 int forward_device_u8(cnn_net* net, const unsigned char* d_pixels, long n, float* d_out, int* d_argmax,
                       cudaStream_t stream) {
-  const int fl = net->fast_sigmoid;
-  return fl == 1 ? launch_variant<1, 2, true>(net, d_pixels, n, d_out, d_argmax, stream)
-       : fl == 2 ? launch_variant<2, 2, true, 2>(net, d_pixels, n, d_out, d_argmax, stream)
-                 : launch_variant<0, 2, true>(net, d_pixels, n, d_out, d_argmax, stream);
+  return net->fast_sigmoid ? launch_variant<2, true, 2>(net, d_pixels, n, d_out, d_argmax, stream)
+                           : launch_variant<0, true, 1>(net, d_pixels, n, d_out, d_argmax, stream);
 }
 
 }  // namespace cnn

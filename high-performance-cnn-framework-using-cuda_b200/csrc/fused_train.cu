@@ -6,8 +6,8 @@
 //    optionally applies the update.  Replaces, per image, forward_pass + makeError + back_pass
 //    (main.cu:67-88, 147-153, 99-119: 17 memsets, 23 launches, one blocking norm).
 //  * k_train_persample -- the reference's learn() loop (main.cu:125-170) as ONE persistent block
-//    (the default is the six-CTA cluster kernel of persample_cluster.cu; this one is selected with
-//    the "persample_cluster" option set to 0):
+//    (the fallback; the default is the six-CTA cluster kernel of persample_cluster8.cu, this one
+//    is selected with the "persample_kernel" option set to 0 and needs no cluster launch):
 //    parameters live in shared memory, one SGD step per image in file order, same update
 //    semantics (output delta without sigmoid derivative, every backward product from pre-update
 //    weights, biases and weights stepped by dt), per-epoch mean of ||delta_f||_2, early stop.
@@ -506,8 +506,7 @@ static int launch_grad_partials(cnn_net* net, const float* d_images, const unsig
                                                              net->d_partials, net->d_status);      \
     }                                                                                              \
   } while (0)
-  if (net->fast_sigmoid == 1) CNN_LAUNCH_GRAD(1);
-  else if (net->fast_sigmoid == 2) CNN_LAUNCH_GRAD(2);
+  if (net->fast_sigmoid) CNN_LAUNCH_GRAD(2);
   else CNN_LAUNCH_GRAD(0);
 #undef CNN_LAUNCH_GRAD
   cudaError_t e = cudaGetLastError();
@@ -553,7 +552,6 @@ int cnn_grad_batch(cnn_net* net, const float* d_images, const unsigned int* d_la
 
 int cnn_apply_update(cnn_net* net, const float* d_grad, float scale, void* stream) {
   CNN_REQUIRE(net && d_grad, "cnn_apply_update: NULL argument");
-  ++net->params_version;
   k_apply_update<<<(kNParams + 255) / 256, 256, 0, as_stream(stream)>>>(net->d_params, d_grad, scale);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_apply_update launch");
@@ -569,7 +567,6 @@ int cnn_train_minibatch(cnn_net* net, const float* d_images, const unsigned int*
   CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
               "cnn_train_minibatch: image batch must start on a 16-byte boundary");
   cudaStream_t st = as_stream(stream);
-  ++net->params_version;
   int rc = ensure_train_scratch(net, 2 * sm_count());
   if (rc != CNN_OK) return rc;
   if (d_mean_err) CNN_CUDA(cudaMemsetAsync(d_mean_err, 0, sizeof(float) * (size_t)epochs, st));
@@ -600,7 +597,6 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
               "cnn_train_sgd_persample: image batch must start on a 16-byte boundary");
   cudaStream_t st = as_stream(stream);
-  ++net->params_version;
   int rc = ensure_train_scratch(net, 2 * sm_count());
   if (rc != CNN_OK) return rc;
   // Scratch reuse: d_grad holds the per-epoch means (epochs <= kNParamsPadded) and the epoch count.
@@ -608,11 +604,8 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
   float* d_mean = net->d_grad;
   int* d_ran = reinterpret_cast<int*>(net->d_grad + kNParamsPadded);
   const size_t smem = sizeof(TrSmem);
-  if (net->ps_cluster == 3) {
+  if (net->ps_kernel) {
     if ((rc = launch_persample_cluster8(net, d_images, d_labels, n, epochs, dt, threshold, d_mean, d_ran, st)) != CNN_OK)
-      return rc;
-  } else if (net->ps_cluster) {
-    if ((rc = launch_persample_cluster(net, d_images, d_labels, n, epochs, dt, threshold, d_mean, d_ran, st)) != CNN_OK)
       return rc;
   } else {
 #define CNN_LAUNCH_PS(FL)                                                                          \
@@ -621,8 +614,7 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
     k_train_persample<FL><<<1, kTrThreads, smem, st>>>(d_images, d_labels, n, epochs, dt, threshold, \
                                                        net->d_params, d_mean, d_ran, net->d_status); \
   } while (0)
-  if (net->fast_sigmoid == 1) CNN_LAUNCH_PS(1);
-  else if (net->fast_sigmoid == 2) CNN_LAUNCH_PS(2);
+  if (net->fast_sigmoid) CNN_LAUNCH_PS(2);
   else CNN_LAUNCH_PS(0);
 #undef CNN_LAUNCH_PS
   }
@@ -662,6 +654,25 @@ constexpr long kNoAllocMaxImages = 65536;     // largest batch the entry point a
 // rows | status word (+ padding to keep the array a multiple of 256 bytes)
 constexpr size_t kNoAllocFloats = (size_t)kNoAllocMaxRows * kRowStride + 64;
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+// Set-up, once per device, with that device current: in host code the array's name is only a
+// handle, its device address has to be asked for.  Also raises the kernel's shared-memory limit.
+static int noalloc_scratch(float** rows) {
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  CNN_CUDA(cudaGetDevice(&dev));
+  CNN_REQUIRE(dev >= 0 && dev < 64, "cnn_grad_batch_noalloc: device ordinal out of range");
+  if (scratch_of_device[dev] == nullptr) {
+    float* ptr = nullptr;
+    CNN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch));
+    CNN_REQUIRE(ptr != nullptr, "cnn_grad_batch_noalloc: no device address for the scratch array");
+    CNN_CUDA(cudaFuncSetAttribute(k_grad_partials<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)sizeof(TrSmem)));
+    scratch_of_device[dev] = ptr;
+  }
+  *rows = scratch_of_device[dev];
+  return CNN_OK;
+}
 }  // namespace cnn
 
 int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const unsigned int* d_labels,
@@ -681,37 +692,44 @@ int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const u
   CNN_REQUIRE(d_images && d_labels, "cnn_grad_batch_noalloc: NULL images or labels");
   CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
               "cnn_grad_batch_noalloc: image batch must start on a 16-byte boundary");
-
-  // Set-up, once per device, with that device current: in host code the array's name is only a
-  // handle, its device address has to be asked for.
-  static float* scratch_of_device[64] = {nullptr};
-  int dev = -1;
-  CNN_CUDA(cudaGetDevice(&dev));
-  CNN_REQUIRE(dev >= 0 && dev < 64, "cnn_grad_batch_noalloc: device ordinal out of range");
-  if (scratch_of_device[dev] == nullptr) {
-    float* ptr = nullptr;
-    CNN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch));
-    CNN_REQUIRE(ptr != nullptr, "cnn_grad_batch_noalloc: no device address for the scratch array");
-    CNN_CUDA(cudaFuncSetAttribute(k_grad_partials<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)sizeof(TrSmem)));
-    scratch_of_device[dev] = ptr;
-  }
-  float* rows = scratch_of_device[dev];
+  float* rows = nullptr;
+  int rc = noalloc_scratch(&rows);
+  if (rc != CNN_OK) return rc;
   int* status = reinterpret_cast<int*>(rows + (size_t)kNoAllocMaxRows * kRowStride);
 
   long grid_l = sm_count();
   if (grid_l > kNoAllocMaxRows) grid_l = kNoAllocMaxRows;
   if (grid_l > n) grid_l = n;
   const int grid = (int)grid_l;
-  // The array keeps what the previous call left: the status word must start at zero (every row that
-  // is read below is rewritten in full by its block, padding included).
-  CNN_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  // The array keeps what the previous call left.  Every row that is read below is rewritten in full
+  // by its block, padding included, so no row needs clearing.  The status word starts at zero when
+  // the library is loaded, is only ever set by a wait that ran out, and stays set until
+  // cnn_grad_batch_noalloc_status reads and clears it.
   k_grad_partials<0, 1><<<grid, kTrThreads, sizeof(TrSmem), st>>>(d_images, d_labels, n, d_params, rows, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch (no-alloc)");
   k_reduce_rows<<<(kNParamsPadded + 31) / 32, 32 * kRedGroups, 0, st>>>(rows, grid, d_grad, nullptr, 0.f, nullptr, 0.f);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_reduce_rows launch (no-alloc)");
+  return CNN_OK;
+}
+
+int cnn_grad_batch_noalloc_status(void* stream) {
+  float* rows = nullptr;
+  int rc = noalloc_scratch(&rows);
+  if (rc != CNN_OK) return rc;
+  int* d_status = reinterpret_cast<int*>(rows + (size_t)kNoAllocMaxRows * kRowStride);
+  cudaStream_t st = as_stream(stream);
+  CNN_CUDA(cudaStreamSynchronize(st));
+  int status = 0;
+  CNN_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+  CNN_CUDA(cudaStreamSynchronize(st));
+  if (status != 0) {
+    CNN_CUDA(cudaMemsetAsync(d_status, 0, sizeof(int), st));
+    CNN_CUDA(cudaStreamSynchronize(st));
+    set_error("cnn_grad_batch_noalloc: a bounded device-side wait ran out; the gradient of that call is not valid");
+    return CNN_ERR_TIMEOUT;
+  }
   return CNN_OK;
 }
 

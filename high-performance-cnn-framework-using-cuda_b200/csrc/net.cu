@@ -1,5 +1,4 @@
 // Fused-network handle: parameter arena, status word, and the host-buffer forward pipeline.
-#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -37,6 +36,7 @@ static int ensure_stage(cnn_net* net) {
     CNN_CUDA(cudaMalloc(&net->d_stage_arg[s], sizeof(int) * kStageImages));
     CNN_CUDA(cudaStreamCreateWithFlags(&net->copy_stream[s], cudaStreamNonBlocking));
   }
+  CNN_CUDA(cudaEventCreateWithFlags(&net->order_event, cudaEventDisableTiming));
   net->stage_images = kStageImages;
   return CNN_OK;
 }
@@ -51,9 +51,7 @@ int cnn_net_create(unsigned int seed, cnn_net** out) {
   *out = nullptr;
   cnn_net* net = new (std::nothrow) cnn_net();
   CNN_REQUIRE(net != nullptr, "cnn_net_create: out of host memory");
-  static std::atomic<int> next_id{0};   // nets may be created from several host threads
-  net->id = next_id.fetch_add(1) + 1;
-  net->const_slot = net->id % 8;
+  net->seed = seed;
   cudaError_t e = cudaGetDevice(&net->device);
   if (e == cudaSuccess) e = cudaMalloc(&net->d_params, sizeof(float) * kNParamsPadded);
   if (e == cudaSuccess) e = cudaMalloc(&net->d_status, sizeof(int));
@@ -100,6 +98,7 @@ int cnn_net_destroy(cnn_net* net) {
     cudaFree(net->d_stage_arg[s]);
     if (net->copy_stream[s]) cudaStreamDestroy(net->copy_stream[s]);
   }
+  if (net->order_event) cudaEventDestroy(net->order_event);
   delete net;
   return CNN_OK;
 }
@@ -112,7 +111,6 @@ int cnn_net_set_params(cnn_net* net, const float* h_params) {
   CNN_CUDA(cudaDeviceSynchronize());
   CNN_CUDA(cudaMemcpy(net->d_params, h_params, sizeof(float) * kNParams, cudaMemcpyHostToDevice));
   CNN_CUDA(cudaDeviceSynchronize());
-  ++net->params_version;
   return CNN_OK;
 }
 
@@ -125,29 +123,29 @@ int cnn_net_get_params(cnn_net* net, float* h_params) {
 int cnn_net_params_device(cnn_net* net, float** d_params) {
   CNN_REQUIRE(net && d_params, "cnn_net_params_device: NULL argument");
   *d_params = net->d_params;
-  ++net->params_version;  // the caller may write through the pointer
   return CNN_OK;
 }
 
 int cnn_net_set_fast_sigmoid(cnn_net* net, int enable) {
   CNN_REQUIRE(net, "cnn_net_set_fast_sigmoid: NULL net");
-  net->fast_sigmoid = (enable == 2) ? 2 : (enable ? 1 : 0);
+  net->fast_sigmoid = enable ? 2 : 0;
   return CNN_OK;
 }
 
 int cnn_net_set_option(cnn_net* net, const char* key, int value) {
   CNN_REQUIRE(net && key, "cnn_net_set_option: NULL argument");
-  if (std::strcmp(key, "fw_variant") == 0) {
-    net->fw_variant = value;
+  if (std::strcmp(key, "persample_kernel") == 0) {
+    CNN_REQUIRE(value == 0 || value == 1, "cnn_net_set_option: persample_kernel takes 0 or 1");
+    net->ps_kernel = value;
     return CNN_OK;
   }
-  if (std::strcmp(key, "persample_cluster") == 0) {
-    CNN_REQUIRE(value >= 0 && value <= 3, "cnn_net_set_option: persample_cluster takes 0 to 3");
-    net->ps_cluster = value;
+  if (std::strcmp(key, "forward_path") == 0) {
+    CNN_REQUIRE(value >= 0 && value <= 2, "cnn_net_set_option: forward_path takes 0, 1 or 2");
+    net->forward_path = value;
     return CNN_OK;
   }
   if (std::strcmp(key, "fast_sigmoid") == 0) {
-    net->fast_sigmoid = (value == 2) ? 2 : (value ? 1 : 0);
+    net->fast_sigmoid = value ? 2 : 0;
     return CNN_OK;
   }
   set_error("cnn_net_set_option: unknown option '%s'", key);
@@ -178,6 +176,13 @@ static int forward_host_impl(cnn_net* net, const void* h_images, bool u8, long n
   const size_t image_bytes = u8 ? (size_t)kImg : sizeof(float) * kImg;
   int rc = ensure_stage(net);
   if (rc != CNN_OK) return rc;
+  // The pipeline runs on two private non-blocking streams.  Both are first put behind everything
+  // queued so far on the legacy default stream (a parameter update, a training call), so that a
+  // forward issued right after such work sees its result; work on a caller's own non-blocking
+  // stream is NOT waited for (the caller synchronises that stream first).
+  CNN_CUDA(cudaEventRecord(net->order_event, cudaStreamLegacy));
+  CNN_CUDA(cudaStreamWaitEvent(net->copy_stream[0], net->order_event, 0));
+  CNN_CUDA(cudaStreamWaitEvent(net->copy_stream[1], net->order_event, 0));
   // Two staging slots, one stream each: within a slot the copy-in, the kernel and the copy-out
   // are stream-ordered; the two slots overlap each other (H2D of chunk c+1 under the kernel and
   // D2H of chunk c).
@@ -225,5 +230,3 @@ int cnn_forward_batched_u8_host(cnn_net* net, const unsigned char* h_pixels, lon
   return forward_host_impl(net, h_pixels, true, n, h_out, h_argmax);
 }
 
-extern "C" {
-}  // extern "C"

@@ -5,16 +5,13 @@
 
 struct cnn_net {
   int device = 0;
-  int id = 0;                      // process-unique, > 0
-  int const_slot = 0;              // constant-bank slot of this net (scalar forward variant)
-  int ps_cluster = 2;              // per-sample SGD: six-CTA cluster kernel with one-way stores (2, default) or
-                                   // hardware cluster barriers (1); 3 = eight outputs per thread and a
-                                   // service warp; 0 = single block
-  long params_version = 1;         // bumped whenever the arena may have changed
+  unsigned seed = 0;               // what cnn_net_create drew the initial parameters from (kept for checkpoints)
+  int ps_kernel = 1;               // per-sample SGD: 1 = six-CTA cluster kernel (default), 0 = single persistent block
+  int forward_path = 0;            // batched forward: 0 = exact fp32 SIMT kernel (default), 1 = tensor cores in three
+                                   // tf32 passes (fp32-level accuracy), 2 = tensor cores, one tf32 pass + tanh sigmoid
   float* d_params = nullptr;       // kNParamsPadded floats
   int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out
-  int fast_sigmoid = 2;            // sigmoid flavour 0 / 1 / 2 (default 2), see sigmoidf in cnn_common.cuh
-  int fw_variant = 0;              // forward kernel: 0 = scalar kernel, two blocks per SM (default); 1, 2, 3 = experiments
+  int fast_sigmoid = 2;            // sigmoid flavour of the fused kernels: 0 (reference expression) or 2 (default)
 
   // Training scratch (allocated on first use): per-block partial gradients and the reduced vector.
   float* d_partials = nullptr;     // [partial_rows][kNParamsPadded]
@@ -26,6 +23,7 @@ struct cnn_net {
   int* d_stage_arg[2] = {nullptr, nullptr};
   long stage_images = 0;
   cudaStream_t copy_stream[2] = {nullptr, nullptr};
+  cudaEvent_t order_event = nullptr;   // host pipeline: ties the two copy streams behind the legacy stream
 };
 
 namespace cnn {
@@ -86,9 +84,5 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 int ensure_train_scratch(cnn_net* net, int rows);
 int launch_persample_cluster8(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
                               float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st);
-int launch_persample_cluster(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
-                             float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st);
-int launch_forward_x2(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
-                      cudaStream_t stream);
 
 }  // namespace cnn

@@ -1,9 +1,17 @@
-// Per-sample SGD (the reference's learn(), main.cu:125-170) on a cluster of six CTAs, variant with
-// eight conv outputs per thread and a service warp (option "persample_cluster" = 3).
+// Per-sample SGD (the reference's learn(), main.cu:125-170) on a thread-block cluster: the default
+// kernel of cnn_train_sgd_persample.
 //
-// Same decomposition as persample_cluster.cu (one feature map per CTA; the FC partial sums and the
-// shared subsample filter's gradient partials cross the cluster as one-way st.async stores counted
-// on the receivers' mbarriers), but the CTA has four warps, one per scheduler of the SM:
+// One SGD step depends on the previous step's parameters, so throughput is 1 / latency of a step.
+// The step is spread over a cluster of six CTAs -- one feature map each -- that exchange only what
+// the maps share: the FC partial sums (before the output layer) and the 17 partial sums of the
+// shared subsample filter's gradient.  Both cross the cluster as one-way st.async stores into the
+// receivers' shared memory, counted on the receivers' mbarriers: no cluster barrier, no release
+// fence; exchange buffers and mbarriers alternate with the sample's parity and the data
+// dependencies alone order buffer reuse.  Everything else (the map's conv filter and bias, its
+// slice of the FC weights) is private to a CTA; the replicated parameters (subsample filter and
+// bias, FC bias) are updated identically in every CTA, so they stay bit-identical.
+//
+// The CTA has four warps, one per scheduler of the SM:
 //   warps 0..2  compute: thread (window, half) owns two rows of a 4x4 subsample window, i.e. eight
 //               conv outputs on a 6x8 patch; 12 windows = 24 live lanes per warp;
 //   warp 3      service: everything serial that is not arithmetic on the patch -- the previous
@@ -20,6 +28,7 @@
 
 #include "cluster_exchange.cuh"
 #include "net.cuh"
+#include "phase_clocks.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -50,22 +59,7 @@ struct C8Smem {
   long long clock_base;         // phase timing only
 };
 
-// Optional phase timing for tuning (off unless the file is compiled with -DCNN_PHASE_CLOCKS): lane 0
-// of every warp of CTA 0 sums, over the samples, the SM clock at each stamp relative to the clock at
-// kernel start; the means per stamp and warp put the four warps on one time axis.
-#ifdef CNN_PHASE_CLOCKS
-__device__ long long g_phase_clocks8[4][16];
-#define CNN_PHASE8(i)                                                    \
-  do {                                                                   \
-    if (f == 0 && lane == 0) {                                           \
-      long long now_;                                                    \
-      asm volatile("mov.u64 %0, %%clock64;" : "=l"(now_)::"memory");     \
-      ph_[i] += now_ - base_;                                            \
-    }                                                                    \
-  } while (0)
-#else
-#define CNN_PHASE8(i) do { } while (0)
-#endif
+CNN_PHASE_TABLE(g_phase_clocks8, 4)
 
 template <int FLAVOR>
 __global__ void __launch_bounds__(kC8Threads, 1)
@@ -119,12 +113,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
   }
   cluster.sync();  // every CTA's shared memory and mbarriers are initialised before anyone sends
 
-#ifdef CNN_PHASE_CLOCKS
-  long long ph_[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  if (tid == 0) sm.clock_base = clock64();
-  __syncthreads();
-  const long long base_ = sm.clock_base;
-#endif
+  CNN_PHASE_BEGIN(f == 0, sm.clock_base)
   bool gave_up = false;
   bool pending = false;    // the previous sample's subsample-gradient exchange has not been consumed yet
   float err = 0.f;         // CTA 0, service lane 0: running sum of the epoch (a float, like main.cu:130)
@@ -163,7 +152,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         next_label = labels[next_im];
       }
       const unsigned label = sm.label[stage];
-      CNN_PHASE8(0);     // top of the loop
+      CNN_PHASE(0);     // top of the loop
 
       // ---- forward: eight conv outputs (rows y0, y0+1; columns x0..x0+3) of map f ------------------
       float pt[6][8];
@@ -207,9 +196,9 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
 #pragma unroll
           for (int c = 0; c < 4; ++c) a[rr][c] = 0.f;
       }
-      CNN_PHASE8(1);     // compute: patch loads, convolution, eight sigmoids
+      CNN_PHASE(1);     // compute: patch loads, convolution, eight sigmoids
       finish_update();   // service warp, under the compute warps' convolution
-      CNN_PHASE8(2);     // at barrier A
+      CNN_PHASE(2);     // at barrier A
       __syncthreads();   // (A) that update is visible; every thread has taken its patch and the label
 
       float wsv[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -256,9 +245,9 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
       }
 
       // ---- (C1) the partial sums of all 18 compute warps have landed here ---------------------------
-      CNN_PHASE8(3);     // compute: subsample, sigmoid, FC partials sent; service: image issued / observed
+      CNN_PHASE(3);     // compute: subsample, sigmoid, FC partials sent; service: image issued / observed
       mbar_wait_cluster_bounded(&sm.fc_bar[stage], (unsigned)(step >> 1) & 1u, status, gave_up);
-      CNN_PHASE8(4);     // exchange complete
+      CNN_PHASE(4);     // exchange complete
       // Expect the next sample's exchanges now: the other barrier pair's previous phases are complete
       // (waited for one sample ago and at the top of this one), and nobody can send for the next
       // sample before this CTA's subsample partials of this one, which go out after barrier B2.
@@ -283,7 +272,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         delta = ((label == (unsigned)lane) ? 1.0f : 0.0f) - o;   // makeError
       }
 
-      CNN_PHASE8(5);     // output layer
+      CNN_PHASE(5);     // output layer
       if (service) {
         // the sample's error norm, while the compute warps run the backward pass
         float sq = delta * delta;   // zero on lanes >= 10
@@ -349,14 +338,14 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
             for (int c = 0; c < 4; ++c) s = fmaf(dc[1][c], pt[1 + ii][c + jj], s);
             g[ii * 5 + jj] = s;
           }
-        CNN_PHASE8(6);   // deltas, subsample gradient, the thread's gradient terms
+        CNN_PHASE(6);   // deltas, subsample gradient, the thread's gradient terms
         g[25] = ((dc[0][0] + dc[0][1]) + (dc[0][2] + dc[0][3])) + ((dc[1][0] + dc[1][1]) + (dc[1][2] + dc[1][3]));
 #pragma unroll
         for (int t = 26; t < 32; ++t) g[t] = 0.f;
         const float mine = warp_reduce_scatter32(g, lane);
         if (lane < 26) sm.c_part[warp][lane] = mine;
       }
-      CNN_PHASE8(7);     // at barrier B2 (compute: reduce-scatter done; service: error norm done)
+      CNN_PHASE(7);     // at barrier B2 (compute: reduce-scatter done; service: error norm done)
       __syncthreads();  // (B2)
 
       if (service) {
@@ -376,7 +365,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         for (int c = 0; c < kClCtas; ++c)
           st_async_f32(cluster_addr(&sm.xws[stage][f][lane], c), sum, cluster_addr(&sm.ws_bar[stage], c));
       }
-      CNN_PHASE8(8);     // at barrier E
+      CNN_PHASE(8);     // at barrier E
       __syncthreads();  // (E) this CTA's updates of wc / bc / bf are ordered before its next convolution
       pending = true;
     }
@@ -413,10 +402,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
     if (tid < kOut) params[kOffBf + tid] = sm.bf[tid];
     if (tid == 0 && epochs_run) *epochs_run = done_epochs;
   }
-#ifdef CNN_PHASE_CLOCKS
-  if (f == 0 && lane == 0)
-    for (int i = 0; i < 16; ++i) g_phase_clocks8[warp][i] = ph_[i];
-#endif
+  CNN_PHASE_END(g_phase_clocks8);
 }
 
 template <int FLAVOR>
@@ -444,11 +430,9 @@ static int launch_cluster8_flavor(const float* d_images, const unsigned* d_label
 
 int launch_persample_cluster8(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
                               float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st) {
-  switch (net->fast_sigmoid) {
-    case 1: return launch_cluster8_flavor<1>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
-    case 2: return launch_cluster8_flavor<2>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
-    default: return launch_cluster8_flavor<0>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
-  }
+  if (net->fast_sigmoid)
+    return launch_cluster8_flavor<2>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
+  return launch_cluster8_flavor<0>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
 }
 
 }  // namespace cnn

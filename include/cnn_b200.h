@@ -129,15 +129,14 @@ int cnn_net_get_params(cnn_net* net, float* h_params);
 /* Device pointer of the arena (CNN_N_PARAMS floats, padded to 2368), for collectives. */
 int cnn_net_params_device(cnn_net* net, float** d_params);
 
-/* Sigmoid flavour of the fused kernels (the per-operator kernels always use flavour 0):
+/* Sigmoid flavour of the fused kernels (the per-operator kernels always use the reference's):
  *   0 = the reference's own expression 1/(1+expf(-v)) with IEEE division (layer.cu:81-84): equal
  *       pre-activations give bit-equal activations, about 21 instructions per evaluation;
- *   1 = __expf / __fdividef, about 1e-6 relative from flavour 0;
- *   2 = (default) two-step argument reduction, ex2.approx and a Newton-refined reciprocal: the same
- *       special-function instruction expf itself is built on; per evaluation a few 1e-7 relative from
- *       flavour 0, on the network's outputs at most 2.0e-6 over 65,536 images
+ *   non-zero (default) = two-step argument reduction, ex2.approx and a Newton-refined reciprocal: the
+ *       same special-function instruction expf itself is built on; per evaluation a few 1e-7 relative
+ *       from flavour 0, on the network's outputs at most 2.0e-6 over 65,536 images
  *       (tests/test_gpu_forward.py::test_sigmoid_flavours_agree measures it), 12 instructions.
- * All three meet the 1e-5 parity bar in every test. */
+ * Both meet the 1e-5 parity bar in every test. */
 int cnn_net_set_fast_sigmoid(cnn_net* net, int enable);
 
 /* Synchronises the device and reports whether any kernel of this net gave up a bounded wait since
@@ -151,7 +150,11 @@ int cnn_forward_batched(cnn_net* net, const float* d_images, long n, float* d_ou
                         void* stream);
 
 /* Same through host buffers: pipelined pinned-or-pageable H2D of the images in chunks, the fused
- * kernel per chunk, D2H of the results; returns after everything has landed. */
+ * kernel per chunk, D2H of the results; returns after everything has landed.  The pipeline runs on
+ * two private streams which are first ordered behind all work queued so far on the legacy default
+ * stream (stream NULL: a cnn_apply_update, cnn_train_minibatch or cnn_grad_batch issued there is
+ * seen).  Work that updates the parameters on a caller's own non-blocking stream is not waited for:
+ * synchronise that stream before this call. */
 int cnn_forward_batched_host(cnn_net* net, const float* h_images, long n, float* h_out,
                              int* h_argmax);
 
@@ -171,13 +174,16 @@ int cnn_forward_batched_u8_host(cnn_net* net, const unsigned char* h_pixels, lon
 int cnn_synth_images(unsigned long long seed, long first_index, long n, float* d_images,
                      unsigned int* d_labels, void* stream);
 
-/* Tuning knobs, by name: "fw_variant" (0 = default scalar forward kernel, two blocks per SM; 1 = the
- * same with one block per SM; 2 = packed-FMA experiment; 3 = constant-bank-weights experiment),
- * "persample_cluster" (kernel of cnn_train_sgd_persample: 2 = default, a cluster of six CTAs that
- * exchange partial sums by one-way stores counted on mbarriers; 1 = the same cluster with hardware
- * cluster barriers, bit-identical results; 3 = the one-way cluster with eight conv outputs per
- * thread and a service warp, the fastest measured, sums in another order so results agree with the
- * default to rounding; 0 = single block), "fast_sigmoid" (as cnn_net_set_fast_sigmoid). */
+/* Options, by name:
+ *   "forward_path"     kernel behind cnn_forward_batched (fp32 images): 0 (default) = exact fp32 on the
+ *                      CUDA cores; 1 = the convolution on the tensor cores (tcgen05) in three tf32
+ *                      passes, fp32-level accuracy, same 1e-5 parity bar; 2 = one tf32 pass and a
+ *                      tanh.approx sigmoid: about 1e-3 on the outputs, argmax equal wherever the
+ *                      top-two margin is clear of that -- an explicitly reduced-precision inference mode;
+ *   "persample_kernel" kernel of cnn_train_sgd_persample: 1 (default) = a cluster of six CTAs, one per
+ *                      feature map, exchanging partial sums by one-way stores counted on mbarriers;
+ *                      0 = one persistent block (no cluster launch needed), about half the speed;
+ *   "fast_sigmoid"     as cnn_net_set_fast_sigmoid. */
 int cnn_net_set_option(cnn_net* net, const char* key, int value);
 
 /* ------------------------------------------------------------------------------------------
@@ -225,9 +231,17 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
  *   - all calls on one device share the one array (it still holds the previous call's rows), so two
  *     calls whose kernels can overlap on the GPU -- different streams, or different host threads --
  *     race; serialise them on one stream or with events;
- *   - the reference sigmoid (flavour 0) is used. */
+ *   - the reference sigmoid (flavour 0) is used;
+ *   - a bounded device-side wait that runs out (never seen in practice: it would mean a bulk copy
+ *     that did not land within seconds) cannot be reported by this asynchronous call; it sets a
+ *     word in the array that cnn_grad_batch_noalloc_status reads. */
 int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const unsigned int* d_labels,
                            long n, float* d_grad, void* stream);
+/* No counterpart in the reference.  Waits for `stream`, then reports whether any
+ * cnn_grad_batch_noalloc call on the current device gave up a bounded wait since the last query
+ * (CNN_ERR_TIMEOUT: the gradient of that call is not valid; the word is cleared), else CNN_OK.
+ * Allocates nothing. */
+int cnn_grad_batch_noalloc_status(void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Widened variant of the same topology: input HxH, F maps of 5x5 -> sigmoid -> one shared 4x4 /
@@ -257,6 +271,19 @@ int cnn_wide_forward(cnn_wide* w, const float* d_images, long n, float* d_out, i
 int cnn_wide_grad_batch(cnn_wide* w, const float* d_images, const unsigned int* d_labels, long n,
                         float* d_grad, void* stream);
 int cnn_wide_apply_update(cnn_wide* w, const float* d_grad, float scale, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Parameter checkpoints.  The reference keeps its parameters only in the device buffers of its
+ * four static Layer objects (main.cu:17-20, filled at layer.cu:19-27) and loses them at exit; these
+ * calls write / read them as a file: little-endian, 32-byte header {magic "CNNB200P", version 1,
+ * kind (0 = 28x28 net, 1 = widened), H, F, parameter count, seed}, the arena as fp32, and a 64-bit
+ * FNV-1a checksum of header + arena.  Loading checks magic, version, shape and checksum and leaves
+ * the net untouched on any mismatch (CNN_ERR_INVALID).  Both calls block.
+ * ---------------------------------------------------------------------------------------- */
+int cnn_net_save(cnn_net* net, const char* path);
+int cnn_net_load(cnn_net* net, const char* path);
+int cnn_wide_save(cnn_wide* w, const char* path);
+int cnn_wide_load(cnn_wide* w, const char* path);
 
 /* Blocking copies between host and device memory (for bindings without a CUDA runtime of their own). */
 int cnn_copy_to_host(void* h_dst, const void* d_src, size_t bytes);

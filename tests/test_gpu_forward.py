@@ -26,21 +26,51 @@ def clear_margin(out, tol=1e-5):
     return (top2[:, -1] - top2[:, -2]) > tol * top2[:, -1]
 
 
-@pytest.mark.parametrize("fast", [0, 1, 2])
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+def check_argmax(arg, ref_arg, ref_out, what, tol=1e-5, max_masked_frac=1e-3):
+    """argmax must equal the oracle's on every row whose top-two margin exceeds ``tol`` relative
+    (below that the reference's own run-to-run atomics order decides the winner); the number of rows
+    excused that way is printed and must be tiny."""
+    ok = clear_margin(ref_out, tol)
+    masked = int((~ok).sum())
+    mism = int((arg != ref_arg).sum())
+    print("%s: %d rows, %d below the %.0e margin, %d argmax differences in all (%d on clear rows)"
+          % (what, len(arg), masked, tol, mism, int((arg[ok] != ref_arg[ok]).sum())))
+    assert np.array_equal(arg[ok], ref_arg[ok])
+    assert masked <= max(1, int(max_masked_frac * len(arg)))
+
+
+@pytest.mark.parametrize("fast", [0, 2])
 @pytest.mark.parametrize("n", [1, 7, 8, 9, 100, 2368 + 5, 4099])
-def test_forward_matches_oracle(cuda, pkg, ob, params0, n, fast, variant):
+def test_forward_matches_oracle(cuda, pkg, ob, params0, n, fast):
     images, _ = pkg.synth.synth_images(21, n)
     net = pkg.Net(0)
     net.set_params(params0)
     net.set_fast_sigmoid(fast)
-    net.set_option("fw_variant", variant)
     out, arg = run_forward(cuda, net, images)
     ref_out, ref_arg = ob.forward_batch(params0, images)
     assert rel_err(out, ref_out) < 1e-5       # the 1e-5 relative bar on activations
-    ok = clear_margin(ref_out)
-    assert np.array_equal(arg[ok], ref_arg[ok])
+    check_argmax(arg, ref_arg, ref_out, "n=%d flavour %d" % (n, fast))
     # the argmax written by the kernel is the lowest-index maximum of the row it wrote
+    assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
+
+
+@pytest.mark.parametrize("fast", [0, 2])
+def test_full_size_forward_matches_oracle(cuda, pkg, ob, params0, fast):
+    """Benchmark configuration 2 at its full size: 65,536 images of seed 1 against the oracle --
+    every sigmoid within 1e-5 relative, argmax equal on every clear-margin row; the number of rows
+    below the margin and the number of differing rows are printed (both are expected to be zero or a
+    handful out of 65,536)."""
+    n = 65536
+    images, _ = pkg.synth.synth_images(1, n)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.set_fast_sigmoid(fast)
+    out, arg = run_forward(cuda, net, images)
+    ref_out, ref_arg = ob.forward_batch(params0, images, threads=0)
+    err = rel_err(out, ref_out)
+    print("full size, flavour %d: max relative error of the sigmoids %.3e" % (fast, err))
+    assert err < 1e-5
+    check_argmax(arg, ref_arg, ref_out, "65,536 images flavour %d" % fast)
     assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
 
 
@@ -120,8 +150,7 @@ def test_forward_against_reference_kernels(cuda, pkg, ob, params0):
         ref_out[i] = ref.read("f", "output")
     ref.close()
     assert rel_err(out, ref_out) < 1e-5
-    ok = clear_margin(ref_out)
-    assert np.array_equal(arg[ok], ref_arg[ok])
+    check_argmax(arg, ref_arg, ref_out, "96 images against the reference kernels", max_masked_frac=0.05)
 
 
 def test_full_size_property_linearity_in_batch(cuda, pkg, params0):
@@ -180,13 +209,13 @@ def test_uint8_input_is_bit_identical_to_fp32(cuda, pkg, params0, n):
 
 
 def test_sigmoid_flavours_agree(cuda, pkg, params0):
-    """Default flavour 2 and the ex2/rcp flavour 1 against the reference expression (flavour 0) on the
-    full benchmark batch: maximum relative difference of the ten outputs."""
+    """The default sigmoid against the reference expression (flavour 0) on the full benchmark batch:
+    maximum relative difference of the ten outputs."""
     n = 65536
     d_img = cuda.empty((n, 28, 28), dtype=cuda.float32, device="cuda")
     pkg.synth_images_device(1, 0, n, d_img)
     outs = {}
-    for fl in (0, 1, 2):
+    for fl in (0, 2):
         net = pkg.Net(0)
         net.set_params(params0)
         net.set_fast_sigmoid(fl)
@@ -195,8 +224,31 @@ def test_sigmoid_flavours_agree(cuda, pkg, params0):
         cuda.cuda.synchronize()
         outs[fl] = o.double()
     d2 = float(((outs[2] - outs[0]).abs() / outs[0]).max())
-    d1 = float(((outs[1] - outs[0]).abs() / outs[0]).max())
-    print("max relative difference to the reference expression: flavour 2 %.3e, flavour 1 %.3e" % (d2, d1))
-    # each flavour is within a few 1e-7 of the exact sigmoid per evaluation (so is libdevice's expf);
-    # three layers deep the outputs differ by up to ~2e-6 in the tails
-    assert d2 < 5e-6 and d1 < 1e-5
+    print("max relative difference to the reference expression: %.3e" % d2)
+    # each evaluation is within a few 1e-7 of the exact sigmoid (so is libdevice's expf); three
+    # layers deep the outputs differ by up to ~2e-6 in the tails
+    assert d2 < 5e-6
+
+
+def test_forward_host_is_ordered_behind_legacy_stream_work(cuda, pkg, params0):
+    """A host-buffer forward issued right after an asynchronous parameter update on the legacy
+    stream (no synchronisation in between) must see the updated parameters."""
+    n = 4096
+    images, labels = pkg.synth.synth_images(27, n)
+    d_img = cuda.from_numpy(images).cuda()
+    d_lab = cuda.from_numpy(labels.astype(np.int32)).cuda()
+    h_img = cuda.from_numpy(images).pin_memory()
+    outs = []
+    for sync_between in (True, False):
+        net = pkg.Net(0)
+        net.set_params(params0)
+        net.forward_host(h_img, 8, None, None)          # staging buffers and streams exist
+        cuda.cuda.synchronize()
+        h_out = cuda.empty((n, 10), dtype=cuda.float32).pin_memory()
+        net.train_minibatch(d_img, d_lab, n, 64, 3, 0.1, None, None)   # asynchronous, stream NULL
+        if sync_between:
+            cuda.cuda.synchronize()
+        net.forward_host(h_img, n, h_out, None)
+        outs.append(h_out.numpy().copy())
+    assert np.array_equal(outs[0], outs[1])
+    assert not np.array_equal(outs[0][:8], 0 * outs[0][:8])

@@ -137,3 +137,37 @@ def test_tensor_core_conv_matches_oracle(cuda, pkg, ob, H, F, n, mode, tol):
     g = d_g.cpu().numpy()
     for name, (lo, hi) in blocks(H, F).items():
         assert scaled_err(g[lo:hi], G[lo:hi]) < tol * (1 if mode == 2 else 10), name
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_wide_full_batch_matches_oracle(cuda, pkg, ob, mode):
+    """Benchmark configuration 5 at its full size (batch 1,024 of 56x56 images, 64 maps) against the
+    generalised oracle: forward outputs within 1e-5 relative, every gradient block within 1e-5 of its
+    largest magnitude, for the fp32 SIMT convolution (conv = 0) and the three-pass tf32 tensor-core
+    convolution (conv = 2)."""
+    H, F, n = 56, 64, 1024
+    x, labels = wide_inputs(n, H, 7)
+    params = wide_params(ob, H, F, 8)
+    net = pkg.WideNet(H, F)
+    net.set_params(params)
+    net.set_option("conv", mode)
+    d_x = cuda.from_numpy(x).cuda()
+    d_lab = cuda.from_numpy(labels.astype(np.int32)).cuda()
+    d_out = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
+    d_arg = cuda.empty((n,), dtype=cuda.int32, device="cuda")
+    net.forward(d_x, n, d_out, d_arg)
+    d_g = cuda.zeros(net.n_padded, dtype=cuda.float32, device="cuda")
+    net.grad_batch(d_x, d_lab, n, d_g)
+    cuda.cuda.synchronize()
+    assert net.status() == 0
+    ref_out, ref_arg = ob.forward_batch(params, x, H=H, F=F, threads=0)
+    assert rel_err(d_out.cpu().numpy(), ref_out) < 1e-5
+    top2 = np.sort(ref_out, axis=1)
+    ok = (top2[:, -1] - top2[:, -2]) > 1e-5 * top2[:, -1]
+    print("conv mode %d: %d of %d rows below the 1e-5 argmax margin" % (mode, int((~ok).sum()), n))
+    assert np.array_equal(d_arg.cpu().numpy()[ok], ref_arg[ok]) and (~ok).sum() <= 2
+    G, err = ob.grad_batch(params, x, labels, H=H, F=F, threads=0)
+    g = d_g.cpu().numpy()
+    for name, (lo, hi) in blocks(H, F).items():
+        assert scaled_err(g[lo:hi], G[lo:hi]) < 1e-5, name
+    assert abs(g[net.n_params + 1] - err) < 1e-5 * max(err, 1.0)
