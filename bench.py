@@ -1,26 +1,32 @@
 #!/usr/bin/env python
-"""Benchmark of the fused forward (the headline), with training legs reported beside it.
+"""Benchmark of the fused forward (the headline), with the other benchmark configurations beside it.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One "step" is one pass of the fused forward kernel over one batch of 65,536 synthetic 28x28 fp32
-images (benchmark configuration 2) per GPU.  At N > 1 (launched by torch.distributed.run, one rank per GPU)
-every rank runs the same per-GPU batch on its own shard of the synthetic stream with no
+images (benchmark configuration 2) per GPU.  At N > 1 (launched by torch.distributed.run, one rank per
+GPU) every rank runs the same per-GPU batch on its own shard of the synthetic stream with no
 communication (inference shards by image; weak scaling), and the time is the max over ranks.
 
 Keys of the JSON line (rank 0 prints exactly one line on stdout):
-  value     images/s with inputs resident in HBM, CUDA-event timed
-  e2e       images/s through cnn_forward_batched_host with pinned HOST buffers: H2D of the images,
-            the kernel and D2H of sigmoids + argmax all inside the timed region
-  roofline  dominant kernel (k_fused_forward) against the measured HBM copy bandwidth, from the
-            algorithmic 3,180 B / image
-  cpu_baseline  the CPU oracle (a C restatement of the reference's kernels; the reference has no
-            CPU implementation of this net) on the host cores, bounded sample
-  train_*   fwd+bwd throughput of the minibatch and per-sample SGD kernels (extra, N-aware)
+  value          images/s with inputs resident in HBM, CUDA-event timed (exact-fp32 kernel)
+  e2e / e2e_u8   images/s through cnn_forward_batched[_u8]_host with pinned HOST buffers: H2D of the
+                 images, the kernel and D2H of sigmoids + argmax all inside the timed region
+  roofline       dominant kernel against the measured HBM copy bandwidth, from the algorithmic
+                 3,180 B / image
+  forward_paths  the same launch through the tensor-core forward kernels (option "forward_path")
+  config1        per-sample SGD, 10,000 images, one epoch, then 2,000 test images (rank 0)
+  config3        16,777,216 images generated on the device, split over the ranks (strong scaling)
+  config4        minibatch SGD, batch 256 per GPU, 60,000 images, ten epochs, gradient exchange fused
+                 into the update kernel (peer stores over NVLink); NCCL timing of the same step beside
+                 it; at N > 1 a parity check (ranks bit-identical, oracle, single-GPU run)
+  config5        widened net, batch 1,024 per GPU, forward + backward + update
+  cpu_baseline   the CPU oracle (a C restatement of the reference's kernels; the reference has no CPU
+                 implementation of this net) on the host cores, bounded samples (N = 1 only)
 
 ``--impl reference`` times the reference path on the host cores (the oracle port with all host
 threads) on the same workload, plus -- when a GPU and the prebuilt unmodified reference kernels are
-present -- the reference's own per-sample CUDA launch sequence as an extra key.
+present -- the reference's own per-sample CUDA launch sequence on configuration 1.
 """
 from __future__ import annotations
 
@@ -43,10 +49,16 @@ BYTES_PER_IMAGE = 3136 + 40 + 4
 FLOP_PER_IMAGE = 184032
 N_ROTATING = 4                # distinct input buffers (4 x 205.5 MB >> 126 MB L2)
 METRIC = "images/sec forward (fused conv-sigmoid-subsample-sigmoid-FC-sigmoid, 28x28 fp32)"
+CONFIG3_IMAGES = 16777216
+CONFIG1_TRAIN, CONFIG1_TEST = 10000, 2000
+CONFIG4_IMAGES, CONFIG4_PER_GPU, CONFIG4_EPOCHS = 60000, 256, 10
 
-
-SIGMOID_NAMES = {0: "reference expression (expf + IEEE divide)", 1: "ex2/rcp approx (~1e-6 rel)",
+SIGMOID_NAMES = {0: "reference expression (expf + IEEE divide)",
                  2: "reduced-argument ex2 + refined rcp (~1e-7 rel)"}
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch over 65,536 images, per forward path,
+# from the ncu captures summarised under profiles/ (k_fused_forward_*, k_forward_tc_*).
+TRAFFIC_BYTES_PER_LAUNCH = {0: 210860000, 1: None, 2: None}
 
 
 def measured_peak_gbs():
@@ -136,12 +148,17 @@ def dist_env():
 
 
 # --------------------------------------------------------------------------------------------------
-# CPU legs (the oracle port; only these functions touch oracle/)
+# CPU legs (the oracle port; only the functions of this section touch oracle/)
 # --------------------------------------------------------------------------------------------------
-def cpu_forward_rate(pkg, params, budget_s: float, threads: int):
-    """images/s of the oracle's batched forward on `threads` host threads over a bounded sample."""
+def _oracle():
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_binding as ob
+    return ob
+
+
+def cpu_forward_rate(pkg, params, budget_s: float, threads: int):
+    """images/s of the oracle's batched forward on `threads` host threads over a bounded sample."""
+    ob = _oracle()
     probe, _ = pkg.synth.synth_images(1, 1024)
     ob.forward_batch(params, probe[:64], threads=threads)          # warm up the thread pool
     t = time.perf_counter()
@@ -155,6 +172,32 @@ def cpu_forward_rate(pkg, params, budget_s: float, threads: int):
     return n / dt, n, dt
 
 
+def cpu_config1(pkg, params):
+    """Benchmark configuration 1 on the CPU oracle, single thread (per-sample SGD is a strict chain):
+    one epoch over 10,000 images, then the 2,000 test images."""
+    ob = _oracle()
+    images, labels = pkg.synth.synth_images(0, CONFIG1_TRAIN + CONFIG1_TEST)
+    t = time.perf_counter()
+    p, mean_err, _ = ob.train_persample(params, images[:CONFIG1_TRAIN], labels[:CONFIG1_TRAIN], 1)
+    sec = time.perf_counter() - t
+    _, arg = ob.forward_batch(p, images[CONFIG1_TRAIN:], threads=1)
+    acc = float((arg == labels[CONFIG1_TRAIN:].astype(np.int32)).mean())
+    return {"train_images_per_s": CONFIG1_TRAIN / sec, "cores": 1, "mean_err": float(mean_err[0]),
+            "test_accuracy": acc, "images": CONFIG1_TRAIN, "test_images": CONFIG1_TEST}, p
+
+
+def cpu_config4_one_epoch(pkg, params, global_batch: int, world: int, images=None, labels=None):
+    """One epoch of benchmark configuration 4 on the CPU oracle (OpenMP over the images of a batch): the timed
+    CPU baseline of minibatch training, and the checker of the data-parallel GPU run."""
+    ob = _oracle()
+    if images is None:
+        images, labels = pkg.synth.synth_images(3, CONFIG4_IMAGES)
+    t = time.perf_counter()
+    p, me = ob.train_minibatch(params, images, labels, global_batch, 1, world=world)
+    sec = time.perf_counter() - t
+    return p, float(me[0]), sec
+
+
 def run_reference_arm(args):
     """The reference path on the host cores: the oracle port (the reference ships no CPU code for
     this net; CNN.py is a different network), all host threads, bounded sample per step."""
@@ -162,8 +205,7 @@ def run_reference_arm(args):
     if rank != 0:
         return
     pkg = entry.load_package()
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import oracle_binding as ob
+    ob = _oracle()
     params = pkg.synth.synth_params(0)
     threads = os.cpu_count() or 1
     probe, _ = pkg.synth.synth_images(1, 2048)
@@ -187,30 +229,37 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(args.steps, 1),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "benchmark configuration 2: fused forward over 65,536 synthetic 28x28 fp32 images",
+        "config": {"workload": "benchmark configuration 2: fused forward, 65,536 synthetic 28x28 fp32 images per GPU per step",
                    "sample_images_per_step": n},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": threads, "kind": "port",
                          "sample": "%d images per step (of 65,536), OpenMP over images on all host threads" % n},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    # Extra: the reference's own per-sample CUDA launch sequence (unmodified layer.cu), when possible.
+    # Extra: benchmark configuration 1 on the CPU port and on the reference's own per-sample CUDA launch sequence
+    # (unmodified layer.cu), the denominator of the per-sample training speed-up.
+    try:
+        c1, _ = cpu_config1(pkg, params)
+        line["config1_cpu_port"] = c1
+    except Exception as e:  # pragma: no cover
+        line["config1_cpu_port"] = {"unavailable": repr(e)[:200]}
     try:
         import torch
         if torch.cuda.is_available() and ob.reference_available():
-            timg, tlab = pkg.synth.synth_images(0, 3000)
+            timg, tlab = pkg.synth.synth_images(0, CONFIG1_TRAIN + CONFIG1_TEST)
             ref = ob.Reference(0)
             ref.set_params(params)
-            ref.time_classify(timg[:200])
-            sec_i, _ = ref.time_classify(timg[:2000])
-            ref.set_params(params)
             ref.time_train(timg[:200], tlab[:200])
+            ref.time_classify(timg[:200])
             ref.set_params(params)
-            sec_t, mean_err = ref.time_train(timg, tlab)
+            sec_t, mean_err = ref.time_train(timg[:CONFIG1_TRAIN], tlab[:CONFIG1_TRAIN])
+            sec_i, preds = ref.time_classify(timg[CONFIG1_TRAIN:])
+            acc = float((preds.astype(np.int64) == tlab[CONFIG1_TRAIN:].astype(np.int64)).mean())
             ref.close()
             line["reference_cuda_path"] = {
-                "what": "unmodified reference kernels, per-sample launch sequence of main.cu (wall clock, device-synchronised)",
-                "infer_images_per_s": 2000 / sec_i, "train_images_per_s": 3000 / sec_t,
-                "train_mean_err": mean_err, "infer_sample": 2000, "train_sample": 3000}
+                "what": "benchmark configuration 1 on the unmodified reference kernels, per-sample launch sequence of "
+                        "main.cu (wall clock, device-synchronised): one epoch over 10,000 images, then 2,000 test images",
+                "train_images_per_s": CONFIG1_TRAIN / sec_t, "infer_images_per_s": CONFIG1_TEST / sec_i,
+                "mean_err": mean_err, "test_accuracy": acc, "images": CONFIG1_TRAIN, "test_images": CONFIG1_TEST}
     except Exception as e:  # pragma: no cover
         line["reference_cuda_path"] = {"unavailable": repr(e)[:200]}
     print(json.dumps(line), flush=True)
@@ -241,20 +290,26 @@ def emit(line: dict) -> None:
         os.write(_REAL_STDOUT_FD, data)
 
 
-def finish(world: int) -> None:
-    """Leave without hanging in library teardown: synchronise, give the process group ten seconds to
-    shut down cleanly, then exit hard (a CUDA graph that holds NCCL kernels made
-    destroy_process_group block on an 8-GPU run)."""
+def shutdown(world: int) -> None:
+    """Orderly end of a rank: everything queued on the device has finished, no CUDA graph is alive,
+    the process group is destroyed, and the interpreter then exits the normal way (exit handlers
+    run).  A watchdog ends the process with a non-zero code if the teardown has not finished after a
+    minute, so a stuck rank cannot hang the job."""
+    import gc
     import torch
+    gc.collect()
     torch.cuda.synchronize()
     sys.stdout.flush()
     sys.stderr.flush()
     if world > 1:
         import torch.distributed as dist
-        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
-        t.start()
-        t.join(timeout=10.0)
-    os._exit(0)
+        watchdog = threading.Timer(60.0, lambda: os._exit(3))
+        watchdog.daemon = True
+        watchdog.start()
+        dist.barrier()
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
+        watchdog.cancel()
 
 
 def run_ours(args):
@@ -296,8 +351,10 @@ def run_ours(args):
     net = pkg.Net(0)
     net.set_params(params)
     net.set_fast_sigmoid(args.fast_sigmoid)
-    net.set_option("fw_variant", args.fw_variant)
+    net.set_option("forward_path", args.forward_path)
     stream = torch.cuda.current_stream()
+    peak, peak_kind = measured_peak_gbs()
+    n_sm = torch.cuda.get_device_properties(local_rank).multi_processor_count
 
     # Each rank owns a contiguous shard of the synthetic stream (seed 1), generated on the device.
     lo, _ = parallel.shard_range(world * N_ROTATING * BATCH, rank, world)
@@ -313,27 +370,28 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     sampler.start()
 
-    def step(i):
-        net.forward(bufs[i % N_ROTATING], BATCH, d_out, d_arg, stream)
+    def time_forward(fnet, steps, warmup):
+        """(total ms over `steps` launches, mean ms per launch) with CUDA events on the launching stream."""
+        for i in range(max(warmup, 3)):
+            fnet.forward(bufs[i % N_ROTATING], BATCH, d_out, d_arg, stream)
+        barrier()
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        events[0].record(stream)
+        for i in range(steps):
+            fnet.forward(bufs[i % N_ROTATING], BATCH, d_out, d_arg, stream)
+            events[i + 1].record(stream)
+        barrier()
+        total = events[0].elapsed_time(events[-1])
+        return total, float(np.mean([events[i].elapsed_time(events[i + 1]) for i in range(steps)]))
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
-    barrier()
-    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     t_clock0 = time.perf_counter()
-    events[0].record(stream)
-    for i in range(args.steps):
-        step(i)
-        events[i + 1].record(stream)
-    barrier()
-    total_ms = events[0].elapsed_time(events[-1])
-    per_launch_ms = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
+    total_ms, kernel_ms = time_forward(net, args.steps, args.warmup)
     # identical untimed continuation so that the 20 ms clock sampler sees the kernel under load
     t_end = time.perf_counter() + (0.0 if args.only_forward else 1.0)
     i = 0
     while time.perf_counter() < t_end:
         for _ in range(50):
-            step(i)
+            net.forward(bufs[i % N_ROTATING], BATCH, d_out, d_arg, stream)
             i += 1
         torch.cuda.synchronize()
     t_clock1 = time.perf_counter()
@@ -342,14 +400,232 @@ def run_ours(args):
 
     total_ms = max_over_ranks(total_ms)
     value = world * BATCH * args.steps / (total_ms * 1e-3)
-    kernel_ms = float(np.mean(per_launch_ms))
-    peak, peak_kind = measured_peak_gbs()
     achieved = BYTES_PER_IMAGE * BATCH / (kernel_ms * 1e-3) / 1e9
     sm_clock_ghz = (clocks.get("sm_mhz") or 1965.0) / 1e3
-    n_sm = torch.cuda.get_device_properties(local_rank).multi_processor_count
     fp32_peak = n_sm * 128 * 2 * sm_clock_ghz * 1e9
 
-    def run_wide_leg(modes=((0, "fp32_simt"), (2, "tf32x3_tcgen05"), (1, "tf32_tcgen05")), steps=5):
+    if args.only_forward:
+        # profiling mode: the forward launches only (used under ncu); prints a reduced line
+        sampler.stop()
+        if rank == 0:
+            emit({"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
+                  "steps": args.steps, "kernel_ms": kernel_ms, "only_forward": True,
+                  "forward_path": args.forward_path})
+        shutdown(world)
+        return
+
+    extra = {}
+
+    # ---- the same launch through the other forward kernels --------------------------------------------
+    def forward_paths_leg():
+        names = {0: "exact fp32 on the CUDA cores (k_fused_forward)",
+                 1: "conv on tcgen05, three tf32 passes (k_forward_tc<1>), 1e-5 parity",
+                 2: "conv on tcgen05, one tf32 pass + tanh.approx sigmoid (k_forward_tc<2>), reduced precision"}
+        res = {}
+        for path in (0, 1, 2):
+            fnet = pkg.Net(0)
+            fnet.set_params(params)
+            fnet.set_fast_sigmoid(args.fast_sigmoid)
+            fnet.set_option("forward_path", path)
+            tot, per = time_forward(fnet, 20, 3)
+            tot = max_over_ranks(tot)
+            assert fnet.status() == 0
+            res["path%d" % path] = {
+                "what": names[path], "images_per_s": world * BATCH * 20 / (tot * 1e-3), "kernel_ms": per,
+                "frac_of_hbm_roofline": BYTES_PER_IMAGE * BATCH / (per * 1e-3) / 1e9 / peak}
+        return res
+
+    # ---- benchmark configuration 3: 16,777,216 images split over the ranks -------------------------------------
+    def config3_leg():
+        lo3, hi3 = parallel.shard_range(CONFIG3_IMAGES, rank, world)
+        cnt = hi3 - lo3
+        d_img3 = torch.empty((cnt, 28, 28), dtype=torch.float32, device="cuda")
+        d_out3 = torch.empty((cnt, 10), dtype=torch.float32, device="cuda")
+        d_arg3 = torch.empty((cnt,), dtype=torch.int32, device="cuda")
+        pkg.synth_images_device(2, lo3, cnt, d_img3, None, stream)
+        torch.cuda.synchronize()
+        res = {}
+        for path in (0, 2):
+            fnet = pkg.Net(0)
+            fnet.set_params(params)
+            fnet.set_option("forward_path", path)
+            fnet.forward(d_img3, min(cnt, 4 * BATCH), d_out3, d_arg3, stream)      # warm-up on a slice
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            fnet.forward(d_img3, cnt, d_out3, d_arg3, stream)
+            e1.record(stream)
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1))
+            assert fnet.status() == 0
+            hist = torch.bincount(d_arg3.long(), minlength=10)
+            if world > 1:
+                dist.all_reduce(hist)
+            res["path%d" % path] = {"images_per_s": CONFIG3_IMAGES / (ms * 1e-3), "ms": ms,
+                                    "frac_of_hbm_roofline": BYTES_PER_IMAGE * CONFIG3_IMAGES / (ms * 1e-3) / 1e9 / (peak * world),
+                                    "argmax_histogram": [int(x) for x in hist.tolist()]}
+        del d_img3, d_out3, d_arg3
+        torch.cuda.empty_cache()
+        return {"what": "benchmark configuration 3: 16,777,216 synthetic images of seed 2 generated on the device, contiguous "
+                        "index ranges over the ranks, no communication; aggregate = images / max-over-ranks time",
+                "images": CONFIG3_IMAGES, "images_per_gpu": cnt, "scaling": "strong", "gpus": world, **res}
+
+    # ---- benchmark configuration 1: per-sample SGD (does not shard: rank 0 only) -------------------------------
+    def config1_leg():
+        d_img1 = torch.empty((CONFIG1_TRAIN + CONFIG1_TEST, 28, 28), dtype=torch.float32, device="cuda")
+        d_lab1 = torch.empty((CONFIG1_TRAIN + CONFIG1_TEST,), dtype=torch.int32, device="cuda")
+        pkg.synth_images_device(0, 0, CONFIG1_TRAIN + CONFIG1_TEST, d_img1, d_lab1, stream)
+        pnet = pkg.Net(0)
+        pnet.set_params(params)
+        pnet.train_sgd_persample(d_img1, d_lab1, 500, 1)
+        best = None
+        for _ in range(3):
+            pnet.set_params(params)
+            t0 = time.perf_counter()
+            ran, mean_err = pnet.train_sgd_persample(d_img1, d_lab1, CONFIG1_TRAIN, 1)
+            sec = time.perf_counter() - t0
+            best = sec if best is None else min(best, sec)
+        d_arg1 = torch.empty((CONFIG1_TEST,), dtype=torch.int32, device="cuda")
+        pnet.forward(d_img1[CONFIG1_TRAIN:], CONFIG1_TEST, None, d_arg1, stream)
+        torch.cuda.synchronize()
+        acc = float((d_arg1 == d_lab1[CONFIG1_TRAIN:]).float().mean().item())
+        return {"what": "benchmark configuration 1: per-sample SGD in file order over 10,000 images (one persistent cluster of "
+                        "six CTAs; does not shard), then argmax over 2,000 test images; labels are uniform random, so "
+                        "accuracy is chance level for every arm",
+                "train_images_per_s": CONFIG1_TRAIN / best, "us_per_sample": 1e6 * best / CONFIG1_TRAIN,
+                "mean_err": float(mean_err[0]), "test_accuracy": acc, "epochs": ran,
+                "images": CONFIG1_TRAIN, "test_images": CONFIG1_TEST}, pnet.get_params()
+
+    # ---- benchmark configuration 4: minibatch SGD, data parallel -----------------------------------------------
+    def config4_leg(oracle_check):
+        n_train, gb = CONFIG4_IMAGES, CONFIG4_PER_GPU * world
+        d_timg = torch.empty((n_train, 28, 28), dtype=torch.float32, device="cuda")
+        d_tlab = torch.empty((n_train,), dtype=torch.int32, device="cuda")
+        pkg.synth_images_device(3, 0, n_train, d_timg, d_tlab, stream)
+        tnet = pkg.Net(0)
+        tnet.set_params(params)
+        dp = pkg.DataParallel(tnet, rank, world, parallel.handle_exchange(dist) if world > 1 else None)
+        d_me = torch.zeros(1, dtype=torch.float32, device="cuda")
+        dp.train_minibatch(d_timg, d_tlab, min(n_train, 8 * gb), gb, 1, 0.1, d_me, stream)      # warm-up
+        barrier()
+        res = {"global_batch": gb, "images": n_train, "epochs": CONFIG4_EPOCHS,
+               "what": "benchmark configuration 4: fused fwd+bwd gradient kernel, then one kernel that reduces the rows, "
+                       "exchanges the 2,368-float vector by peer stores over NVLink, adds the ranks in fixed order "
+                       "and applies the update" if world > 1 else
+                       "benchmark configuration 4: fused fwd+bwd gradient kernel, then one reduce + update kernel (single GPU)"}
+        # One epoch = one CUDA graph (two kernels per step): a step is a few microseconds of GPU work.
+        tnet.set_params(params)
+        graph = None
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    dp.train_minibatch(d_timg, d_tlab, n_train, gb, 1, 0.1, d_me, torch.cuda.current_stream())
+            torch.cuda.current_stream().wait_stream(side)
+            res["launch"] = "each epoch replayed as one CUDA graph"
+
+            def run_epoch():
+                graph.replay()
+        except Exception as ge:  # pragma: no cover
+            graph = None
+            res["launch"] = "eager launches (graph capture failed: %s)" % repr(ge)[:120]
+
+            def run_epoch():
+                dp.train_minibatch(d_timg, d_tlab, n_train, gb, 1, 0.1, d_me, stream)
+
+        # parity: one epoch from the initial parameters
+        barrier()
+        tnet.set_params(params)
+        run_epoch()
+        torch.cuda.synchronize()
+        assert tnet.status() == 0
+        p1 = torch.from_numpy(tnet.get_params()).cuda()
+        if world > 1:
+            allp = [torch.empty_like(p1) for _ in range(world)]
+            dist.all_gather(allp, p1)
+            identical = all(torch.equal(allp[0], a) for a in allp)
+        else:
+            identical = True
+        check = {"ranks_bit_identical_after_one_epoch": bool(identical)}
+        if rank == 0 and oracle_check is not None:
+            p_or, me_or = oracle_check
+            scale = float(np.max(np.abs(p_or)))
+            check["vs_oracle_params"] = float(np.max(np.abs(p1.cpu().numpy() - p_or)) / scale)
+            check["mean_err_epoch1"] = float(d_me.item())
+            check["oracle_mean_err_epoch1"] = me_or
+            check["within_2e-5_of_oracle"] = bool(check["vs_oracle_params"] < 2e-5)
+        if rank == 0 and world > 1:
+            single = pkg.Net(0)
+            single.set_params(params)
+            single.train_minibatch(d_timg, d_tlab, n_train, gb, 1, 0.1, None, stream)
+            torch.cuda.synchronize()
+            p_s = single.get_params()
+            check["vs_single_gpu_same_global_batch"] = float(np.max(np.abs(p1.cpu().numpy() - p_s)) / float(np.max(np.abs(p_s))))
+        res["parity"] = check
+        assert identical, "data-parallel ranks diverged"
+
+        # timing: ten epochs from the initial parameters
+        tnet.set_params(params)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        me_hist = torch.zeros(CONFIG4_EPOCHS, dtype=torch.float32, device="cuda")
+        e0.record(stream)
+        for ep in range(CONFIG4_EPOCHS):
+            run_epoch()
+            me_hist[ep:ep + 1].copy_(d_me)
+        e1.record(stream)
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1))
+        assert tnet.status() == 0
+        steps_per_epoch = (n_train + gb - 1) // gb
+        d_targ = torch.empty((CONFIG1_TEST,), dtype=torch.int32, device="cuda")
+        tnet.forward(d_timg, CONFIG1_TEST, None, d_targ, stream)
+        torch.cuda.synchronize()
+        res.update({"images_per_s": CONFIG4_EPOCHS * n_train / (ms * 1e-3), "ms": ms,
+                    "us_per_step": 1e3 * ms / (CONFIG4_EPOCHS * steps_per_epoch), "steps_per_epoch": steps_per_epoch,
+                    "mean_err_per_epoch": [float(x) for x in me_hist.cpu().tolist()],
+                    "train_accuracy_first_2000": float((d_targ == d_tlab[:CONFIG1_TEST]).float().mean().item()),
+                    "frac_of_hbm_roofline": (3140 * CONFIG4_EPOCHS * n_train / (ms * 1e-3) / 1e9) / (peak * world)})
+        graph = None     # nothing captured stays alive past this leg
+        dp.close()
+
+        # the portable fallback beside it: the same step with NCCL's all-reduce (eager launches)
+        if world > 1:
+            fnet = pkg.Net(0)
+            fnet.set_params(params)
+            d_grad = torch.zeros(2368, dtype=torch.float32, device="cuda")
+            trainer = parallel.DataParallelTrainer(
+                rank, world, lambda a, b, out: fnet.grad_batch(d_timg[a:], d_tlab[a:], b - a, out, stream),
+                lambda g, s: fnet.apply_update(g, s, stream), lambda t: dist.all_reduce(t), d_grad, dt=0.1)
+            trainer.epoch(8 * gb, gb)
+            barrier()
+            e0.record(stream)
+            steps_n = trainer.epoch(n_train, gb)
+            e1.record(stream)
+            barrier()
+            ms_n = max_over_ranks(e0.elapsed_time(e1))
+            res["nccl_fallback"] = {"images_per_s": n_train / (ms_n * 1e-3), "us_per_step": 1e3 * ms_n / steps_n,
+                                    "what": "gradient kernel, row reduction, NCCL all-reduce of 2,368 floats, update; eager launches, one epoch"}
+        if rank == 0:
+            big = 57344
+            fnet = pkg.Net(0)
+            fnet.set_params(params)
+            d_grad = torch.zeros(2368, dtype=torch.float32, device="cuda")
+            fnet.grad_batch(d_timg, d_tlab, big, d_grad, stream)
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(5):
+                fnet.grad_batch(d_timg, d_tlab, big, d_grad, stream)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            msb = e0.elapsed_time(e1) / 5
+            res["grad_large_batch"] = {"images_per_s": big / (msb * 1e-3), "batch": big,
+                                       "frac_of_hbm_roofline": (3140 * big / (msb * 1e-3) / 1e9) / peak}
+        return res
+
+    def config5_leg(modes=((0, "fp32_simt"), (2, "tf32x3_tcgen05"), (1, "tf32_tcgen05")), steps=5):
         """benchmark configuration 5: widened net (56x56 input, 64 maps), batch 1,024 per GPU, fwd+bwd+update."""
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wide_batch = 1024
@@ -383,24 +659,16 @@ def run_ours(args):
             wide[name] = {"images_per_s": wide_batch * world / (ms * 1e-3), "ms_per_step": ms,
                           "tflops": 18992896.0 * wide_batch * world / (ms * 1e-3) / 1e12}
         assert wnet.status() == 0
-        return {"what": "benchmark configuration 5: 56x56 input, 64 maps, batch 1,024 per GPU, "
-                                            "fwd+bwd+update" + (", NCCL all-reduce of 109,856 floats" if world > 1 else ""),
-                                    "conv": wide}
+        return {"what": "benchmark configuration 5: 56x56 input, 64 maps, batch 1,024 per GPU, fwd+bwd+update"
+                        + (", NCCL all-reduce of 109,856 floats" if world > 1 else ""), "conv": wide}
 
     if args.only_wide:
-        res = run_wide_leg(modes=((args.only_wide - 1, "conv_mode_%d" % (args.only_wide - 1)),), steps=args.steps)
+        res = config5_leg(modes=((args.only_wide - 1, "conv_mode_%d" % (args.only_wide - 1)),), steps=args.steps)
         sampler.stop()
         if rank == 0:
-            emit({"only_wide": True, "train_wide_cfg5": res})
-        finish(world)
-
-    if args.only_forward:
-        # profiling mode: the forward launches only (used under ncu); prints a reduced line
-        sampler.stop()
-        if rank == 0:
-            emit({"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
-                  "steps": args.steps, "kernel_ms": kernel_ms, "only_forward": True})
-        finish(world)
+            emit({"only_wide": True, "config5": res})
+        shutdown(world)
+        return
 
     e2e_value = e2e_u8_value = None
     e2e_steps = 0
@@ -432,161 +700,102 @@ def run_ours(args):
         torch.cuda.synchronize()
         e2e_u8_value = world * BATCH * e2e_steps / max_over_ranks(time.perf_counter() - t0)
         barrier()
+        del h_img, h_pix
 
-    # ---- extra: training legs -------------------------------------------------------------------
-    train = {}
-    try:
-        n_train = 60000
-        per_gpu_batch = 256
-        lo_t, hi_t = parallel.shard_range(n_train, 0, 1)
-        d_timg = torch.empty((n_train, 28, 28), dtype=torch.float32, device="cuda")
-        d_tlab = torch.empty((n_train,), dtype=torch.int32, device="cuda")
-        pkg.synth_images_device(3, 0, n_train, d_timg, d_tlab, stream)
-        tnet = pkg.Net(0)
-        tnet.set_params(params)
-        d_grad = torch.zeros(2368, dtype=torch.float32, device="cuda")
-        gb = per_gpu_batch * world
-
-        def grad_fn(a, b, out):
-            tnet.grad_batch(d_timg[a:], d_tlab[a:], b - a, out, stream)
-
-        trainer = parallel.DataParallelTrainer(
-            rank, world, grad_fn, lambda g, s: tnet.apply_update(g, s, stream),
-            (lambda t: dist.all_reduce(t)) if world > 1 else None, d_grad, dt=0.1)
-        trainer.epoch(min(n_train, 20 * gb), gb)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        # One epoch = one CUDA graph (gradient kernel, row reduction, all-reduce, update per step):
-        # the step is a few microseconds of GPU work, so launch latency would otherwise dominate.
-        graph_note = "epoch captured in one CUDA graph"
+    # ---- CPU legs first where a GPU leg is checked against them (rank 0) ---------------------------------
+    cpu = None
+    oracle_check = None
+    cpu_extra = {}
+    if rank == 0 and not args.only_train:
         try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                cap_stream = torch.cuda.current_stream()
-                trainer.grad_fn = lambda a, b, out: tnet.grad_batch(d_timg[a:], d_tlab[a:], b - a, out, cap_stream)
-                trainer.update_fn = lambda g, s: tnet.apply_update(g, s, cap_stream)
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=side):
-                    steps_t = trainer.epoch(n_train, gb)
-            torch.cuda.current_stream().wait_stream(side)
-            graph.replay()
-            barrier()
-            e0.record(stream)
-            graph.replay()
-            e1.record(stream)
-        except Exception as ge:  # pragma: no cover
-            graph_note = "eager launches (graph capture failed: %s)" % repr(ge)[:120]
-            trainer.grad_fn = grad_fn
-            trainer.update_fn = lambda g, s: tnet.apply_update(g, s, stream)
-            torch.cuda.synchronize()
-            e0.record(stream)
-            steps_t = trainer.epoch(n_train, gb)
-            e1.record(stream)
+            threads = os.cpu_count() or 1
+            if world == 1:
+                rate, n_s, dt = cpu_forward_rate(pkg, params, 6.0, threads)
+                cpu = {"value": rate, "unit": "images/s", "cores": threads, "kind": "port",
+                       "sample": "%d of 65,536 images, %.1f s, OpenMP over images (C restatement of layer.cu; "
+                                 "the reference has no CPU code for this net)" % (n_s, dt)}
+                r1, n1, dt1 = cpu_forward_rate(pkg, params, 2.0, 1)
+                cpu["forward_single_thread"] = {"images_per_s": r1, "cores": 1, "sample": "%d images, %.1f s" % (n1, dt1)}
+                c1, _ = cpu_config1(pkg, params)
+                cpu["config1_persample_sgd"] = c1
+            p_or, me_or, sec = cpu_config4_one_epoch(pkg, params, CONFIG4_PER_GPU * world, world)
+            oracle_check = (p_or, me_or)
+            cpu_extra = {"images_per_s": CONFIG4_IMAGES / sec, "cores": threads, "mean_err_epoch1": me_or,
+                         "sample": "one epoch of 60,000 images, global batch %d, OpenMP over the images of a batch, %.1f s"
+                                   % (CONFIG4_PER_GPU * world, sec)}
+            if cpu is not None:
+                cpu["config4_minibatch"] = cpu_extra
+        except Exception as e:  # pragma: no cover
+            extra["cpu_legs_error"] = repr(e)[:300]
+    barrier()
+
+    for name, leg in (("forward_paths", forward_paths_leg), ("config3", config3_leg)):
+        if args.only_train:
+            continue
+        try:
+            extra[name] = leg()
+        except Exception as e:  # pragma: no cover
+            extra[name] = {"error": repr(e)[:300]}
         barrier()
-        ms = max_over_ranks(e0.elapsed_time(e1))
-        graph = None   # drop the captured epoch (it holds NCCL kernels) before anything else runs
-        train["train_minibatch"] = {
-            "images_per_s": n_train / (ms * 1e-3), "global_batch": gb, "steps": steps_t,
-            "us_per_step": 1e3 * ms / steps_t, "images": n_train, "launch": graph_note,
-            "what": "benchmark configuration 4, one epoch: fused fwd+bwd gradient kernel, %s, update"
-                    % ("NCCL all-reduce of 2,368 floats" if world > 1 else "single GPU (no collective)"),
-            "frac_of_hbm_roofline": (3140 * n_train / (ms * 1e-3) / 1e9) / (peak * world)}
-        if rank == 0:
-            # large-batch fwd+bwd throughput (compute-bound shape of the same kernel)
-            big = 57344
-            tnet.grad_batch(d_timg, d_tlab, big, d_grad, stream)
-            torch.cuda.synchronize()
-            e0.record(stream)
-            for _ in range(5):
-                tnet.grad_batch(d_timg, d_tlab, big, d_grad, stream)
-            e1.record(stream)
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / 5
-            train["train_grad_large_batch"] = {"images_per_s": big / (ms * 1e-3), "batch": big,
-                                               "frac_of_hbm_roofline": (3140 * big / (ms * 1e-3) / 1e9) / peak}
-            # per-sample SGD, benchmark configuration 1: 10,000 images, one epoch, one persistent six-CTA cluster
-            pnet = pkg.Net(0)
-            pnet.set_params(params)
-            pnet.train_sgd_persample(d_timg, d_tlab, 500, 1)
-            pnet.set_params(params)
-            t0 = time.perf_counter()
-            ran, mean_err = pnet.train_sgd_persample(d_timg, d_tlab, 10000, 1)
-            sec = time.perf_counter() - t0
-            train["train_persample"] = {"images_per_s": 10000 / sec, "images": 10000, "epochs": ran,
-                                        "mean_err": float(mean_err[0]),
-                                        "what": "benchmark configuration 1: per-sample SGD in file order, one persistent cluster of six CTAs (does not shard)"}
-            # the same through the option that selects the variant with eight outputs per thread and a
-            # service warp (cnn_net_set_option "persample_cluster" = 3)
-            pnet.set_option("persample_cluster", 3)
-            pnet.set_params(params)
-            pnet.train_sgd_persample(d_timg, d_tlab, 500, 1)
-            pnet.set_params(params)
-            t0 = time.perf_counter()
-            ran, mean_err = pnet.train_sgd_persample(d_timg, d_tlab, 10000, 1)
-            sec = time.perf_counter() - t0
-            train["train_persample_option3"] = {"images_per_s": 10000 / sec, "images": 10000, "epochs": ran,
-                                                "mean_err": float(mean_err[0]),
-                                                "what": "the same with option persample_cluster = 3 (eight conv outputs per thread, service warp)"}
-        barrier()
-        if not args.only_train:
-            train["train_wide_cfg5"] = run_wide_leg()
-        barrier()
+    if rank == 0:
+        try:
+            extra["config1"], _ = config1_leg()
+        except Exception as e:  # pragma: no cover
+            extra["config1"] = {"error": repr(e)[:300]}
+    barrier()
+    try:
+        extra["config4"] = config4_leg(oracle_check)
+        if world > 1 and cpu_extra:
+            extra["config4"]["cpu_port_one_epoch"] = cpu_extra
     except Exception as e:  # pragma: no cover
-        train["train_error"] = repr(e)[:300]
+        extra["config4"] = {"error": repr(e)[:300]}
+    barrier()
+    if not args.only_train:
+        try:
+            extra["config5"] = config5_leg()
+        except Exception as e:  # pragma: no cover
+            extra["config5"] = {"error": repr(e)[:300]}
+        barrier()
 
     sampler.stop()
 
     if args.only_train:
         if rank == 0:
-            emit({"only_train": True, **train})
-        finish(world)
+            emit({"only_train": True, **extra})
+        shutdown(world)
+        return
 
-    if rank != 0:
-        finish(world)
-
-    cpu = None
-    if world == 1:
-        threads = os.cpu_count() or 1
-        rate, n_s, dt = cpu_forward_rate(pkg, params, 12.0, threads)
-        cpu = {"value": rate, "unit": "images/s", "cores": threads, "kind": "port",
-               "sample": "%d of 65,536 images, %.1f s, OpenMP over images (C restatement of layer.cu; "
-                         "the reference has no CPU code for this net)" % (n_s, dt)}
-
-    line = {
-        "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "benchmark configuration 2: fused forward, 65,536 synthetic 28x28 fp32 images per GPU per step",
-                   "images_per_gpu_per_step": BATCH, "global_images_per_step": BATCH * world,
-                   "l2": "inputs rotate over %d distinct 205.5 MB buffers (> 126 MB L2)" % N_ROTATING,
-                   "sigmoid": SIGMOID_NAMES[args.fast_sigmoid],
-                   "fw_variant": args.fw_variant, "parallelism": "shard by image, no collective"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
-                     "peak_kind": "of " + peak_kind, "kernel": "k_fused_forward",
-                     "kernel_ms": kernel_ms, "algorithmic_bytes_per_image": BYTES_PER_IMAGE,
-                     "binding_limit": "fp32 FMA + MUFU pipes, not HBM (58 FLOP/B)",
-                     "fp32_fma_frac": FLOP_PER_IMAGE * BATCH / (kernel_ms * 1e-3) / fp32_peak},
-        "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": BATCH * 3136,
-                "d2h_bytes_per_step": BATCH * 44, "steps": e2e_steps,
-                "api": "cnn_forward_batched_host (pinned host buffers, 8,192-image chunks on two streams)"},
-        "e2e_u8": {"value": e2e_u8_value, "unit": "images/s", "h2d_bytes_per_step": BATCH * 784,
-                   "d2h_bytes_per_step": BATCH * 44, "api": "cnn_forward_batched_u8_host (uint8 pixels, "
-                   "pixel/255.0 applied in the kernel; bit-identical results)"},
-        "gpu_launches": args.steps * world,
-        "clocks": clocks,
-    }
-    if cpu:
-        line["cpu_baseline"] = cpu
-    line.update(train)
-    emit(line)
-    finish(world)
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_fused_forward launch over 65,536 images,
-# from the ncu capture summarised in profiles/k_fused_forward_cfg2_65536_images.md.
-TRAFFIC_BYTES_PER_LAUNCH = 211743488
+    if rank == 0:
+        kernel_names = {0: "k_fused_forward", 1: "k_forward_tc<1>", 2: "k_forward_tc<2>"}
+        line = {
+            "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "benchmark configuration 2: fused forward, 65,536 synthetic 28x28 fp32 images per GPU per step",
+                       "images_per_gpu_per_step": BATCH, "global_images_per_step": BATCH * world,
+                       "l2": "inputs rotate over %d distinct 205.5 MB buffers (> 126 MB L2)" % N_ROTATING,
+                       "sigmoid": SIGMOID_NAMES[2 if args.fast_sigmoid else 0],
+                       "forward_path": args.forward_path, "parallelism": "shard by image, no collective"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(args.forward_path),
+                         "peak_kind": "of " + peak_kind, "kernel": kernel_names[args.forward_path],
+                         "kernel_ms": kernel_ms, "algorithmic_bytes_per_image": BYTES_PER_IMAGE,
+                         "binding_limit": "fp32 FMA + MUFU pipes, not HBM (58 FLOP/B)",
+                         "fp32_fma_frac": FLOP_PER_IMAGE * BATCH / (kernel_ms * 1e-3) / fp32_peak},
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": BATCH * 3136,
+                    "d2h_bytes_per_step": BATCH * 44, "steps": e2e_steps,
+                    "api": "cnn_forward_batched_host (pinned host buffers, 8,192-image chunks on two streams)"},
+            "e2e_u8": {"value": e2e_u8_value, "unit": "images/s", "h2d_bytes_per_step": BATCH * 784,
+                       "d2h_bytes_per_step": BATCH * 44, "api": "cnn_forward_batched_u8_host (uint8 pixels, "
+                       "pixel/255.0 applied in the kernel; bit-identical results)"},
+            "gpu_launches": args.steps * world,
+            "clocks": clocks,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        line.update(extra)
+        emit(line)
+    shutdown(world)
 
 
 def main():
@@ -596,7 +805,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--fast-sigmoid", type=int, default=2)
-    ap.add_argument("--fw-variant", type=int, default=0)
+    ap.add_argument("--forward-path", type=int, default=0,
+                    help="kernel of the headline: 0 exact fp32 SIMT, 1 tcgen05 three tf32 passes, 2 tcgen05 one pass + tanh")
     ap.add_argument("--only-train", type=int, default=0,
                     help="run only the training legs of the reference net (for ncu launch lists)")
     ap.add_argument("--only-wide", type=int, default=0,

@@ -116,6 +116,15 @@ _PROTOTYPES = {
     "cnn_grad_batch": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
     "cnn_grad_batch_noalloc": (C.c_int, [_P, _P, _P, C.c_long, _P, _P]),
     "cnn_grad_batch_noalloc_status": (C.c_int, [_P]),
+    "cnn_dp_create": (C.c_int, [_P, C.c_int, C.c_int, C.POINTER(_P)]),
+    "cnn_dp_destroy": (C.c_int, [_P]),
+    "cnn_dp_export_handle": (C.c_int, [_P, _P]),
+    "cnn_dp_connect": (C.c_int, [_P, _P]),
+    "cnn_dp_local_buffer": (C.c_int, [_P, C.POINTER(_P)]),
+    "cnn_dp_connect_pointers": (C.c_int, [_P, C.POINTER(_P)]),
+    "cnn_dp_set_option": (C.c_int, [_P, C.c_char_p, C.c_int]),
+    "cnn_dp_step": (C.c_int, [_P, _P, _P, C.c_long, C.c_float, _P, _P, C.c_float, _P]),
+    "cnn_train_minibatch_dp": (C.c_int, [_P, _P, _P, C.c_long, C.c_long, C.c_int, C.c_float, _P, _P]),
     "cnn_net_save": (C.c_int, [_P, C.c_char_p]),
     "cnn_net_load": (C.c_int, [_P, C.c_char_p]),
     "cnn_wide_save": (C.c_int, [_P, C.c_char_p]),
@@ -396,6 +405,62 @@ class Net:
     def close(self) -> None:
         if getattr(self, "_h", None) is not None:
             load_library().cnn_net_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class DataParallel:
+    """Minibatch SGD of a ``Net`` across the GPUs of one box with the gradient exchange fused into
+    the update kernel (``cnn_dp_*``): one instance per rank, each on its own device.
+
+    ``exchange`` is a callable that takes this rank's 64-byte handle and returns the list of all
+    ranks' handles in rank order (e.g. ``torch.distributed.all_gather_object``); it is not needed
+    for a single rank."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, net: "Net", rank: int = 0, world: int = 1, exchange=None):
+        lib = load_library()
+        self.net, self.rank, self.world = net, rank, world
+        h = _P()
+        _check(lib.cnn_dp_create(net._h, rank, world, C.byref(h)))
+        self._h = h
+        if world > 1:
+            if exchange is None:
+                raise ValueError("exchange is required when world > 1")
+            mine = (C.c_ubyte * self.HANDLE_BYTES)()
+            _check(lib.cnn_dp_export_handle(self._h, C.cast(mine, _P)))
+            handles = exchange(bytes(mine))
+            if len(handles) != world or any(len(x) != self.HANDLE_BYTES for x in handles):
+                raise ValueError("exchange must return one %d-byte handle per rank" % self.HANDLE_BYTES)
+            blob = (C.c_ubyte * (self.HANDLE_BYTES * world)).from_buffer_copy(b"".join(handles))
+            _check(lib.cnn_dp_connect(self._h, C.cast(blob, _P)))
+        else:
+            _check(lib.cnn_dp_connect(self._h, None))
+
+    def set_option(self, key: str, value: int) -> None:
+        _check(load_library().cnn_dp_set_option(self._h, key.encode(), int(value)))
+
+    def step(self, d_images, d_labels, n_local: int, scale: float, d_grad_sum=None, d_mean_err=None,
+             err_scale: float = 0.0, stream=None) -> None:
+        _check(load_library().cnn_dp_step(self._h, _ptr(d_images), _ptr(d_labels), int(n_local), float(scale),
+                                          _ptr(d_grad_sum), _ptr(d_mean_err), float(err_scale), _stream(stream)))
+
+    def train_minibatch(self, d_images, d_labels, n: int, global_batch: int, epochs: int, dt: float = 0.1,
+                        d_mean_err=None, stream=None) -> None:
+        """Every rank passes the same n images; see ``cnn_train_minibatch_dp``."""
+        _check(load_library().cnn_train_minibatch_dp(self._h, _ptr(d_images), _ptr(d_labels), int(n),
+                                                     int(global_batch), int(epochs), float(dt),
+                                                     _ptr(d_mean_err), _stream(stream)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None:
+            load_library().cnn_dp_destroy(self._h)
             self._h = None
 
     def __del__(self):

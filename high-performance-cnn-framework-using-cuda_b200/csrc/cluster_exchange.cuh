@@ -23,6 +23,16 @@ __device__ __forceinline__ void st_async_f32(unsigned remote_addr, float v, unsi
                "r"(__float_as_uint(v)), "r"(remote_bar)
                : "memory");
 }
+// The same for four consecutive floats (16-byte aligned): one transaction on the receiver's mbarrier
+// instead of four.
+__device__ __forceinline__ void st_async_f32x4(unsigned remote_addr, float a, float b, float c, float d,
+                                               unsigned remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
+                   remote_addr),
+               "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(__float_as_uint(c)), "r"(__float_as_uint(d)),
+               "r"(remote_bar)
+               : "memory");
+}
 // Non-blocking test (test_wait, not try_wait): the exchange waits sit on the critical path of every
 // sample and a suspended try_wait was seen to resume late.
 __device__ __forceinline__ bool mbar_try_wait_cluster(unsigned long long* bar, unsigned parity) {

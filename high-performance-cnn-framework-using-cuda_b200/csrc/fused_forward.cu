@@ -223,6 +223,7 @@ static int launch_variant(cnn_net* net, const void* d_images, long n, float* d_o
 // chains in flight at the same 96 registers); three-fold unrolling spills.
 int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                    cudaStream_t stream) {
+  if (net->forward_path != 0) return forward_device_tc(net, d_images, n, d_out, d_argmax, stream);
   return net->fast_sigmoid ? launch_variant<2, false, 2>(net, d_images, n, d_out, d_argmax, stream)
                            : launch_variant<0, false, 1>(net, d_images, n, d_out, d_argmax, stream);
 }

@@ -163,8 +163,6 @@ __device__ __forceinline__ void thread_backward(const TrSmem& sm, const FwdRegs&
 // Row layout (kRowStride floats): arena-ordered gradient [0, 2343), zero padding, and at
 // kRowErr the sum over the block's images of ||delta_f||_2.
 // ----------------------------------------------------------------------------------------------
-constexpr int kRowStride = kNParamsPadded + 8;
-constexpr int kRowErr = kNParams + 1;  // 2344
 
 // MINB = 1: one block per SM, no register cap -- lowest latency, used for small batches.
 // MINB = 2: two blocks per SM at 128 registers -- higher throughput on large batches.
@@ -490,7 +488,7 @@ static int set_smem_attr(K kernel, size_t bytes) {
   return CNN_OK;
 }
 
-static int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_labels, long n,
+int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_labels, long n,
                                 int grid, cudaStream_t st) {
   const size_t smem = sizeof(TrSmem);
   int rc;
@@ -515,7 +513,7 @@ static int launch_grad_partials(cnn_net* net, const float* d_images, const unsig
 }
 
 // Small batches: one block per SM (latency).  From 8 images per SM on: two blocks per SM (throughput).
-static int grid_for_batch(long n) {
+int grid_for_batch(long n) {
   const long sms = sm_count();
   const long cap = (n >= 8 * sms) ? 2 * sms : sms;
   return (int)(n < cap ? n : cap);

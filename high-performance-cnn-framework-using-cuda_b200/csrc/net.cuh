@@ -81,7 +81,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
   return true;
 }
 
+// Partial-gradient rows of the minibatch kernels: arena-ordered gradient [0, 2343), zero padding,
+// and at kRowErr the sum over the row's images of ||delta_f||_2.
+constexpr int kRowStride = kNParamsPadded + 8;
+constexpr int kRowErr = kNParams + 1;  // 2344
+
+// Batched forward with the convolution on the tensor cores (forward_tc.cu): net->forward_path 1 or 2.
+int forward_device_tc(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+                      cudaStream_t stream);
 int ensure_train_scratch(cnn_net* net, int rows);
+// Blocks of the minibatch gradient kernel for a batch of n images (one partial row per block).
+int grid_for_batch(long n);
+// Fused forward + backward of n images at fixed parameters: `grid` partial rows into net->d_partials.
+int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int grid,
+                         cudaStream_t st);
 int launch_persample_cluster8(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
                               float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st);
 

@@ -34,6 +34,15 @@ namespace cg = cooperative_groups;
 
 namespace cnn {
 
+// Sigmoid behind fast_sigmoid != 0.  This kernel is a chain of dependent latencies (three sigmoids in
+// sequence per sample), so it takes the short form -- ex2.approx and rcp.approx, four dependent
+// instructions, about 1e-6 relative per evaluation -- instead of the refined twelve-instruction one
+// of the throughput kernels: measured 1.646 against 1.714 us per sample, with the same distance from
+// the oracle after 2,000 steps (1.2e-5 of the largest parameter, set by summation order).
+#ifndef CNN_PS_FAST_FLAVOR
+#define CNN_PS_FAST_FLAVOR 1
+#endif
+constexpr int kC8FastFlavor = CNN_PS_FAST_FLAVOR;
 constexpr int kC8Threads = 128;
 constexpr int kC8Compute = 3;                 // compute warps
 constexpr int kC8WinPerWarp = 12;
@@ -47,7 +56,8 @@ struct C8Smem {
   float bs[4];
   float wf[kOut][36];           // Wf[k][this map][window]
   float bf[12];
-  float xfc[2][kClCtas][kC8Compute][12];   // FC partial sums of every compute warp of every CTA
+  float xfc[2][kClCtas][kC8Compute][16];   // FC partial sums of every compute warp of every CTA: outputs 0..4 at
+                                           // [0..4], outputs 5..9 at [8..12] (two 16-byte aligned halves)
   float c_part[kC8Compute][28]; // per-warp conv-filter gradient partials (25) + conv-bias partial
   float s_part[kC8Compute][20]; // per-warp subsample-filter gradient partials (16) + bias partial
   float xws[2][kClCtas][20];    // subsample gradient partials of every CTA
@@ -223,11 +233,11 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         }
         zs += __shfl_xor_sync(0xffffffffu, zs, 1);
         as = sigmoidf<FLAVOR>(zs + sm.bs[0]);
-        // FC: the window's two lanes split the outputs, k = half + 2j; then the warp's windows
+        // FC: the window's two lanes split the outputs, k = 5 * half + j; then the warp's windows
         float pk[5];
 #pragma unroll
         for (int j = 0; j < 5; ++j) {
-          wfk[j] = live ? sm.wf[half + 2 * j][win] : 0.f;
+          wfk[j] = live ? sm.wf[5 * half + j][win] : 0.f;
           pk[j] = wfk[j] * as;
         }
 #pragma unroll
@@ -235,12 +245,13 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
 #pragma unroll
           for (int j = 0; j < 5; ++j) pk[j] += __shfl_xor_sync(0xffffffffu, pk[j], m);
         // every lane now holds the warp's sums for its five outputs: lane 2c + half sends them to CTA c
+        // as one 16-byte store and one 4-byte store (two transactions on the receiver's mbarrier)
         if (lane < 2 * kClCtas) {
           const unsigned dst = (unsigned)(lane >> 1);
           const unsigned bar = cluster_addr(&sm.fc_bar[stage], dst);
-#pragma unroll
-          for (int j = 0; j < 5; ++j)
-            st_async_f32(cluster_addr(&sm.xfc[stage][f][warp][half + 2 * j], dst), pk[j], bar);
+          const unsigned to = cluster_addr(&sm.xfc[stage][f][warp][8 * half], dst);
+          st_async_f32x4(to, pk[0], pk[1], pk[2], pk[3], bar);
+          st_async_f32(to + 16u, pk[4], bar);
         }
       }
 
@@ -264,7 +275,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         for (int c = 0; c < kClCtas; ++c) {
           float zc = 0.f;
 #pragma unroll
-          for (int ww = 0; ww < kC8Compute; ++ww) zc += sm.xfc[stage][c][ww][lane];
+          for (int ww = 0; ww < kC8Compute; ++ww) zc += sm.xfc[stage][c][ww][lane < 5 ? lane : lane + 3];
           z += zc;
         }
         z += sm.bf[lane];
@@ -283,7 +294,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         // ---- backward ----------------------------------------------------------------------------
         float d[5];
 #pragma unroll
-        for (int j = 0; j < 5; ++j) d[j] = __shfl_sync(0xffffffffu, delta, half + 2 * j);
+        for (int j = 0; j < 5; ++j) d[j] = __shfl_sync(0xffffffffu, delta, 5 * half + j);
         float das = wfk[0] * d[0];
 #pragma unroll
         for (int j = 1; j < 5; ++j) das = fmaf(wfk[j], d[j], das);
@@ -291,7 +302,7 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         const float delta_s = live ? das * as * (1.f - as) : 0.f;
         if (live) {
 #pragma unroll
-          for (int j = 0; j < 5; ++j) sm.wf[half + 2 * j][win] = fmaf(dt, d[j] * as, wfk[j]);  // bp_weight_f + apply_grad
+          for (int j = 0; j < 5; ++j) sm.wf[5 * half + j][win] = fmaf(dt, d[j] * as, wfk[j]);  // bp_weight_f + apply_grad
         }
         // subsample filter gradient: this thread's two filter rows, reduce-scattered over the warp's
         // 16 window slots (lane bits 4, 3, 2 pick the element, bit 1 is summed last); bias term
@@ -431,7 +442,7 @@ static int launch_cluster8_flavor(const float* d_images, const unsigned* d_label
 int launch_persample_cluster8(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
                               float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st) {
   if (net->fast_sigmoid)
-    return launch_cluster8_flavor<2>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
+    return launch_cluster8_flavor<kC8FastFlavor>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
   return launch_cluster8_flavor<0>(d_images, d_labels, n, epochs, dt, threshold, net->d_params, d_mean, d_ran, net->d_status, st);
 }
 

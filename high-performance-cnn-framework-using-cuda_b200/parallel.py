@@ -11,6 +11,11 @@ The reference is single-GPU (no collective anywhere in layer.cu / main.cu).  Two
 
 Per-sample SGD does not shard: each step needs the previous step's parameters.
 
+Two exchange mechanisms exist for the training path.  The default on GPUs is the library's own
+(``DataParallel`` in the package: the exchange is fused into the update kernel as peer stores over
+NVLink, see ``csrc/dp_exchange.cu``); ``DataParallelTrainer`` below is the portable fallback that
+calls an injected all-reduce (NCCL on GPUs, gloo in the CPU tests).
+
 The gradient function and the update function are injected, so the same driver runs on GPUs
 (``Net`` methods + NCCL) and, in the CPU tests, on ``gloo`` ranks.
 """
@@ -35,6 +40,16 @@ def batch_plan(n: int, global_batch: int):
     if global_batch <= 0:
         raise ValueError("global_batch must be positive")
     return [(first, min(global_batch, n - first)) for first in range(0, n, global_batch)]
+
+
+def handle_exchange(dist):
+    """An ``exchange`` callable for ``DataParallel``: all-gathers one bytes object per rank through
+    ``torch.distributed`` (any backend) and returns them in rank order."""
+    def exchange(handle: bytes):
+        out = [None] * dist.get_world_size()
+        dist.all_gather_object(out, handle)
+        return out
+    return exchange
 
 
 class DataParallelTrainer:

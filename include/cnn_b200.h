@@ -244,6 +244,49 @@ int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const u
 int cnn_grad_batch_noalloc_status(void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Data-parallel minibatch SGD over the GPUs of one box (one host thread or process per GPU).  No
+ * counterpart in the reference, which trains on a single GPU (main.cu:125-170 is its whole loop and
+ * there is no collective in layer.cu / main.cu); the per-step arithmetic is cnn_train_minibatch's.
+ * Every rank computes the summed gradient of its slice of a global batch; one kernel per step then
+ * reduces the rank's partial rows, stores the 2368-float vector into a per-source slot of every
+ * rank's exchange buffer (ordinary stores through peer-mapped memory over NVLink, then a release
+ * flag), waits -- bounded -- on its own buffer for all ranks' contributions, adds them in rank order
+ * and applies params += (dt / global_batch) * sum.  All ranks add the same values in the same order,
+ * so their parameters stay bit-identical.  A wait that runs out (a rank that never sent) leaves the
+ * parameters of that step untouched and is reported by cnn_net_status as CNN_ERR_TIMEOUT.
+ *
+ * Set-up: cnn_dp_create on every rank (allocates the rank's exchange buffer on the current device),
+ * then either exchange the 64-byte handles of cnn_dp_export_handle between PROCESSES by any host
+ * channel and pass all of them, in rank order, to cnn_dp_connect (CUDA IPC), or, for ranks that are
+ * THREADS of one process, pass the pointers of cnn_dp_local_buffer to cnn_dp_connect_pointers (peer
+ * access between the devices must be enabled by the caller).  world <= 8.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct cnn_dp cnn_dp;
+#define CNN_DP_HANDLE_BYTES 64
+int cnn_dp_create(cnn_net* net, int rank, int world, cnn_dp** out);
+int cnn_dp_destroy(cnn_dp* dp);
+int cnn_dp_export_handle(cnn_dp* dp, void* handle /* CNN_DP_HANDLE_BYTES */);
+int cnn_dp_connect(cnn_dp* dp, const void* handles /* world * CNN_DP_HANDLE_BYTES, rank order */);
+int cnn_dp_local_buffer(cnn_dp* dp, void** d_buffer);
+int cnn_dp_connect_pointers(cnn_dp* dp, void* const* d_buffers /* world device pointers, rank order */);
+/* "wait_limit_ms" (default 2000): bound of the device-side waits for the other ranks.
+ * "drop_next_send" = 1: host-side fault injection for tests -- the next step of this rank sends
+ * nothing, so every rank's wait runs out and reports CNN_ERR_TIMEOUT. */
+int cnn_dp_set_option(cnn_dp* dp, const char* key, int value);
+/* One step: gradient of this rank's n_local images (may be 0), exchange, params += scale * sum over
+ * all ranks.  d_grad_sum (2368 floats, may be NULL) receives the all-rank sum; if d_mean_err is given,
+ * *d_mean_err += err_scale * (all-rank sum of the error norms).  Asynchronous on `stream`; every rank
+ * must call it the same number of times. */
+int cnn_dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels, long n_local, float scale,
+                float* d_grad_sum, float* d_mean_err, float err_scale, void* stream);
+/* cnn_train_minibatch across the ranks: d_images / d_labels hold ALL n images on every rank; of each
+ * global batch of `global_batch` images (the last may be smaller) rank r takes the contiguous slice
+ * [size*r/world, size*(r+1)/world).  d_mean_err (device, `epochs` floats, may be NULL) receives the
+ * per-epoch mean error norm over all n images, identical on every rank.  Asynchronous on `stream`. */
+int cnn_train_minibatch_dp(cnn_dp* dp, const float* d_images, const unsigned int* d_labels, long n,
+                           long global_batch, int epochs, float dt, float* d_mean_err, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Widened variant of the same topology: input HxH, F maps of 5x5 -> sigmoid -> one shared 4x4 /
  * stride-4 filter -> sigmoid -> FC F*P*P -> 10 -> sigmoid (C = H-4, P = C/4).  The reference's
  * kernels are fixed to 28x28 / 6 maps (layer.h:45-62); this is the same operator sequence

@@ -60,6 +60,10 @@ def test_subsample_gradient_reduce_scatter_lands_on_the_storing_lane():
 
 
 def test_fc_partial_sums_reach_every_cta():
+    """A window's two lanes split the ten outputs (lane half h takes k = 5h .. 5h+4); after the
+    butterfly over the warp's windows lane 2c + h holds those five sums and stores them into CTA c's
+    buffer row of 16 floats at [8h .. 8h+4] (one 16-byte and one 4-byte one-way store); the receiver's
+    lane k < 10 reads slot k (k < 5) or k + 3."""
     rng = np.random.default_rng(1)
     half = LANES & 1
     live = (LANES >> 1) < WINDOWS_PER_WARP
@@ -68,11 +72,17 @@ def test_fc_partial_sums_reach_every_cta():
     terms = pk.copy()
     for m in (2, 4, 8, 16):
         pk = pk + pk[:, LANES ^ m]
-    want = np.array([terms[k // 2][half == k % 2].sum() for k in range(10)])
-    got = np.full((6, 10), np.nan)
+    want = np.array([terms[k % 5][half == k // 5].sum() for k in range(10)])
+    row = np.full((6, 16), np.nan)
+    stores = 0
     for lane in range(12):
-        for j in range(5):
-            got[lane >> 1][(lane & 1) + 2 * j] = pk[j][lane]
+        c, h = lane >> 1, lane & 1
+        assert (8 * h * 4) % 16 == 0                      # the 16-byte store is aligned
+        row[c][8 * h:8 * h + 4] = pk[0:4, lane]
+        row[c][8 * h + 4] = pk[4][lane]
+        stores += 2
+    got = np.array([[row[c][k if k < 5 else k + 3] for k in range(10)] for c in range(6)])
     assert np.allclose(got, want[None, :])
+    assert stores == 24                                   # per warp; 60 with one store per float
     # bytes counted on a receiver's mbarrier per sample: 6 CTAs x 3 warps x 10 floats
     assert 6 * COMPUTE_WARPS * 10 * 4 == 720

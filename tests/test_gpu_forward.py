@@ -252,3 +252,66 @@ def test_forward_host_is_ordered_behind_legacy_stream_work(cuda, pkg, params0):
         outs.append(h_out.numpy().copy())
     assert np.array_equal(outs[0], outs[1])
     assert not np.array_equal(outs[0][:8], 0 * outs[0][:8])
+
+
+# ---- the convolution on the tensor cores (option "forward_path") ------------------------------------
+@pytest.mark.parametrize("fast", [0, 2])
+@pytest.mark.parametrize("n", [1, 5, 16, 17, 100, 2368 + 5, 4099])
+def test_tensor_core_forward_three_passes_matches_oracle(cuda, pkg, ob, params0, n, fast):
+    """forward_path = 1: tcgen05 convolution in three tf32 passes keeps the 1e-5 bar of the fp32 path."""
+    images, _ = pkg.synth.synth_images(21, n)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.set_fast_sigmoid(fast)
+    net.set_option("forward_path", 1)
+    out, arg = run_forward(cuda, net, images)
+    ref_out, ref_arg = ob.forward_batch(params0, images)
+    assert rel_err(out, ref_out) < 1e-5
+    check_argmax(arg, ref_arg, ref_out, "tensor cores, three passes, n=%d flavour %d" % (n, fast))
+    assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
+
+
+def test_tensor_core_forward_full_size(cuda, pkg, ob, params0):
+    """Benchmark configuration 2 at full size on both tensor-core paths.  Path 1 (three passes): 1e-5
+    on every sigmoid, argmax on every clear-margin row.  Path 2 (one tf32 pass, tanh.approx sigmoid) is
+    a reduced-precision mode: its bar is 5e-3 absolute on the sigmoids and argmax equality on every
+    row whose top-two margin is clear of that error (1e-2 relative); both counts are printed."""
+    n = 65536
+    images, _ = pkg.synth.synth_images(1, n)
+    ref_out, ref_arg = ob.forward_batch(params0, images, threads=0)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.set_option("forward_path", 1)
+    out, arg = run_forward(cuda, net, images)
+    err = rel_err(out, ref_out)
+    print("three passes: max relative error of the sigmoids %.3e" % err)
+    assert err < 1e-5
+    check_argmax(arg, ref_arg, ref_out, "65,536 images, tensor cores, three passes")
+    # bit-repeatable, and independent of where an image sits in the batch
+    out2, arg2 = run_forward(cuda, net, images[1000:3000])
+    assert np.array_equal(out2, out[1000:3000]) and np.array_equal(arg2, arg[1000:3000])
+    net.set_option("forward_path", 2)
+    out, arg = run_forward(cuda, net, images)
+    abs_err = float(np.max(np.abs(out.astype(np.float64) - ref_out)))
+    print("one pass + tanh: max absolute error of the sigmoids %.3e, mean %.3e"
+          % (abs_err, float(np.mean(np.abs(out.astype(np.float64) - ref_out)))))
+    assert abs_err < 5e-3
+    check_argmax(arg, ref_arg, ref_out, "65,536 images, tensor cores, one pass + tanh", tol=1e-2,
+                 max_masked_frac=0.05)
+    assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
+
+
+def test_tensor_core_forward_optional_outputs_and_host_pipeline(cuda, pkg, params0):
+    n = 8192 + 300
+    images, _ = pkg.synth.synth_images(28, n)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.set_option("forward_path", 1)
+    out, arg = run_forward(cuda, net, images)
+    o2, _ = run_forward(cuda, net, images, want_arg=False)
+    _, a2 = run_forward(cuda, net, images, want_out=False)
+    assert np.array_equal(o2, out) and np.array_equal(a2, arg)
+    h_out = np.empty((n, 10), dtype=np.float32)
+    h_arg = np.empty((n,), dtype=np.int32)
+    net.forward_host(images, n, h_out, h_arg)
+    assert np.array_equal(h_out, out) and np.array_equal(h_arg, arg)

@@ -161,13 +161,24 @@ def test_wide_full_batch_matches_oracle(cuda, pkg, ob, mode):
     cuda.cuda.synchronize()
     assert net.status() == 0
     ref_out, ref_arg = ob.forward_batch(params, x, H=H, F=F, threads=0)
-    assert rel_err(d_out.cpu().numpy(), ref_out) < 1e-5
+    # The FC of this net adds 10,816 products: two fp32 evaluations in different orders already differ
+    # by more than 1e-5 on some of the 10,240 outputs, so the judge here is the fp64 oracle -- 1e-5, or
+    # twice the fp32 oracle's own distance from it where that is larger.
+    ref64, _ = ob.forward_batch(params, x, H=H, F=F, threads=0, dtype=np.float64)
+    e_lib, e_or = rel_err(d_out.cpu().numpy(), ref64), rel_err(ref_out, ref64)
+    print("conv mode %d: outputs against the fp64 oracle: library %.3e, fp32 oracle %.3e" % (mode, e_lib, e_or))
+    assert e_lib < max(1e-5, 2 * e_or)
     top2 = np.sort(ref_out, axis=1)
     ok = (top2[:, -1] - top2[:, -2]) > 1e-5 * top2[:, -1]
     print("conv mode %d: %d of %d rows below the 1e-5 argmax margin" % (mode, int((~ok).sum()), n))
     assert np.array_equal(d_arg.cpu().numpy()[ok], ref_arg[ok]) and (~ok).sum() <= 2
+    # gradients: sums over 1,024 images (and 2,704 positions for the conv filter) -- the fp64 oracle
+    # judges, with the fp32 oracle's own distance from it as the floor of what fp32 can deliver
     G, err = ob.grad_batch(params, x, labels, H=H, F=F, threads=0)
+    G64, err64 = ob.grad_batch(params, x, labels, H=H, F=F, threads=0, dtype=np.float64)
     g = d_g.cpu().numpy()
     for name, (lo, hi) in blocks(H, F).items():
-        assert scaled_err(g[lo:hi], G[lo:hi]) < 1e-5, name
-    assert abs(g[net.n_params + 1] - err) < 1e-5 * max(err, 1.0)
+        e_lib, e_or = scaled_err(g[lo:hi], G64[lo:hi]), scaled_err(G[lo:hi], G64[lo:hi])
+        print("  %s: library %.3e, fp32 oracle %.3e (against the fp64 oracle)" % (name, e_lib, e_or))
+        assert e_lib < max(1e-5, 2 * e_or), name
+    assert abs(g[net.n_params + 1] - err64) < 1e-5 * max(err64, 1.0)
