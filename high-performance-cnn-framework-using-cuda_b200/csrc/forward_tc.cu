@@ -28,8 +28,8 @@
 //   warp 0      bulk copies (cp.async.bulk, no multicast) of 136 stacked rows = 15,232 contiguous
 //               bytes per tile into a raw staging buffer, three stages;
 //   warps 2-3   rearrange a raw tile into the operand layout (and split it, path 1);
-//   warp 1      one thread issues the tile's MMAs into one of three 160-column accumulators and
-//               commits to an mbarrier;
+//   warp 1      issues the tile's MMAs into one of three 160-column accumulators and commits to an
+//               mbarrier (the whole warp runs the loop, an elected lane issues: see wide_tc.cuh);
 //   warps 4-15  three epilogue groups of four warps (one per 32-lane quarter of tensor memory), one
 //               tile each: tcgen05.ld of 24 columns (one window column, six maps) at a time, bias,
 //               sigmoid, the window row's four subsample taps; the four rows of a window are four
@@ -65,6 +65,7 @@ struct TfSmem {
   alignas(128) unsigned char b_hi[kTfBBytes];
   alignas(128) unsigned char b_lo[kTfBBytes];                        // path 1 only
   alignas(16) float wf[7][36][12];          // [window row p][6 * q + f][k], p = 6 is the junk row (zeros)
+  float wf_tail[12];                        // a lane's empty fifth slot may read one entry past the last row
   alignas(16) float part[kTfSlots][6][12];  // FC partial sums of (image slot, window row)
   int done[kTfSlots];                       // window rows of the slot's image that have arrived
   float bc[8], ws[16], bs[4], bf[12];
@@ -179,41 +180,40 @@ k_forward_tc(const float* __restrict__ images, long n, long imgs_per_cta, const 
       }
     }
   } else if (warp == 1) {
-    // ================= MMA issue ==================================================================
-    if (lane == 0) {
-      const unsigned idesc = tc::idesc_tf32(kTfRows, kTfBN, 0, 0);
-      const unsigned b_hi_s = smem_u32(sm.b_hi), b_lo_s = smem_u32(sm.b_lo);
-      for (int k = 0; k < n_tiles; ++k) {
-        const int s = k % kTfStages;
-        const unsigned par = (unsigned)(k / kTfStages) & 1u;
-        mbar_wait_bounded(&sm.a_full[s], par, status, gave_up);
-        mbar_wait_bounded(&sm.d_free[s], par ^ 1u, status, gave_up);
-        tc::fence_after_sync();
-        const unsigned a_hi_s = smem_u32(sm.a_hi[s]), a_lo_s = smem_u32(sm.a_lo[s]);
-        const unsigned d_tile = tmem_base + (unsigned)(s * kTfDCols);
-        constexpr int kPasses = kPrecise ? 3 : 1;
+    // ================= MMA issue: the whole warp runs the loop, one elected lane issues ============
+    const unsigned idesc = tc::idesc_tf32(kTfRows, kTfBN, 0, 0);
+    const unsigned b_hi_s = smem_u32(sm.b_hi), b_lo_s = smem_u32(sm.b_lo);
+    for (int k = 0; k < n_tiles; ++k) {
+      const int s = k % kTfStages;
+      const unsigned par = (unsigned)(k / kTfStages) & 1u;
+      mbar_wait_bounded(&sm.a_full[s], par, status, gave_up);
+      mbar_wait_bounded(&sm.d_free[s], par ^ 1u, status, gave_up);
+      __syncwarp();
+      tc::fence_after_sync();
+      const unsigned a_hi_s = smem_u32(sm.a_hi[s]), a_lo_s = smem_u32(sm.a_lo[s]);
+      const unsigned d_tile = tmem_base + (unsigned)(s * kTfDCols);
+      constexpr int kPasses = kPrecise ? 3 : 1;
 #pragma unroll
-        for (int xb = 0; xb < 2; ++xb) {
-          unsigned accumulate = 0;
+      for (int xb = 0; xb < 2; ++xb) {
+        unsigned accumulate = 0;
 #pragma unroll
-          for (int pass = 0; pass < kPasses; ++pass) {
-            const unsigned a_s = (pass == 1) ? a_lo_s : a_hi_s;
-            const unsigned b_s = (pass == 2) ? b_lo_s : b_hi_s;
+        for (int pass = 0; pass < kPasses; ++pass) {
+          const unsigned a_s = (pass == 1) ? a_lo_s : a_hi_s;
+          const unsigned b_s = (pass == 2) ? b_lo_s : b_hi_s;
 #pragma unroll
-            for (int i = 0; i < 5; ++i) {
+          for (int i = 0; i < 5; ++i) {
 #pragma unroll
-              for (int ks = 0; ks < 2; ++ks) {
-                const unsigned long long ad =
-                    tc::smem_desc(a_s + (unsigned)(3 * xb + 2 * ks) * kTfChunkStride + (unsigned)i * 16u, kTfChunkStride, 128);
-                const unsigned long long bd = tc::smem_desc(b_s + (unsigned)i * kTfBRow + (unsigned)(2 * ks) * kTfBChunk, kTfBChunk, 128);
-                tc::mma_tf32(d_tile + (unsigned)(xb * kTfBN), ad, bd, idesc, accumulate);
-                accumulate = 1;
-              }
+            for (int ks = 0; ks < 2; ++ks) {
+              const unsigned long long ad =
+                  tc::smem_desc(a_s + (unsigned)(3 * xb + 2 * ks) * kTfChunkStride + (unsigned)i * 16u, kTfChunkStride, 128);
+              const unsigned long long bd = tc::smem_desc(b_s + (unsigned)i * kTfBRow + (unsigned)(2 * ks) * kTfBChunk, kTfBChunk, 128);
+              tc::mma_tf32_elect(d_tile + (unsigned)(xb * kTfBN), ad, bd, idesc, accumulate);
+              accumulate = 1;
             }
           }
         }
-        tc::mma_commit(&sm.d_full[s]);
       }
+      tc::mma_commit_elect(&sm.d_full[s]);
     }
   } else if (warp < kTfEpiWarp0) {
     // ================= converters: raw tile -> operand slab(s) ====================================
@@ -279,78 +279,86 @@ k_forward_tc(const float* __restrict__ images, long n, long imgs_per_cta, const 
       const bool valid = (img_l < imgs_here) && (p < 6);
       const unsigned t0 = tmem_base + (unsigned)(group * kTfDCols) + ((unsigned)(quarter * 32) << 16);
 
-      float z[36];
+      float fc[kOut];
+#pragma unroll
+      for (int kk = 0; kk < kOut; ++kk) fc[kk] = 0.f;
+      const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
+      const int pw = p < 6 ? p : 6;                 // the junk window row reads the table's zero row
+
       unsigned ra[8], rb[8], rc[8], na[8], nb[8], nc[8];
       tmem_ld8_nowait(t0 + 0, ra);
       tmem_ld8_nowait(t0 + 8, rb);
       tmem_ld8_nowait(t0 + 16, rc);
       tmem_wait24(ra, rb, rc);
 #pragma unroll
-      for (int wq = 0; wq < 6; ++wq) {              // window column q = wq: block wq / 3, 24 columns at a time
-        if (wq + 1 < 6) {
-          const unsigned c0 = (unsigned)(((wq + 1) / 3) * kTfBN + ((wq + 1) % 3) * 24);
-          tmem_ld8_nowait(t0 + c0, na);
-          tmem_ld8_nowait(t0 + c0 + 8, nb);
-          tmem_ld8_nowait(t0 + c0 + 16, nc);
-        } else {
-          // the last columns of this accumulator are in registers: hand it back to the MMA warp
-          tc::fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.d_free[group]);
-        }
+      for (int xb = 0; xb < 2; ++xb) {              // one 12-column block = three window columns
+        float z[18];
 #pragma unroll
-        for (int f = 0; f < kF; ++f) {
-          float acc = 0.f;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int c = f * 4 + j;
-            const unsigned bits = (c < 8) ? ra[c] : (c < 16) ? rb[c - 8] : rc[c - 16];
-            const float v = __uint_as_float(bits) + bcr[f];
-            const float a = kPrecise ? sigmoidf<SIG>(v) : tanh_approx(v);
-            acc = fmaf(wsr[j], a, acc);
+        for (int wq = 0; wq < 3; ++wq) {            // window column q = 3 * xb + wq: 24 accumulator columns
+          const int nxt = 3 * xb + wq + 1;
+          if (nxt < 6) {
+            const unsigned c0 = (unsigned)((nxt / 3) * kTfBN + (nxt % 3) * 24);
+            tmem_ld8_nowait(t0 + c0, na);
+            tmem_ld8_nowait(t0 + c0 + 8, nb);
+            tmem_ld8_nowait(t0 + c0 + 16, nc);
+          } else {
+            // the last columns of this accumulator are in registers: hand it back to the MMA warp
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.d_free[group]);
           }
-          z[wq * 6 + f] = acc;
+          // 24 independent activations, written in stages so that their chains interleave
+          float av[24];
+#pragma unroll
+          for (int c = 0; c < 24; ++c) {
+            const unsigned bits = (c < 8) ? ra[c] : (c < 16) ? rb[c - 8] : rc[c - 16];
+            av[c] = __uint_as_float(bits) + bcr[c >> 2];
+          }
+#pragma unroll
+          for (int c = 0; c < 24; ++c) av[c] = kPrecise ? sigmoidf<SIG>(av[c]) : tanh_approx(av[c]);
+#pragma unroll
+          for (int f = 0; f < kF; ++f)
+            z[wq * 6 + f] = fmaf(wsr[3], av[f * 4 + 3], fmaf(wsr[2], av[f * 4 + 2], fmaf(wsr[1], av[f * 4 + 1], wsr[0] * av[f * 4])));
+          if (nxt < 6) {
+            tmem_wait24(na, nb, nc);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { ra[e] = na[e]; rb[e] = nb[e]; rc[e] = nc[e]; }
+          }
         }
-        if (wq + 1 < 6) {
-          tmem_wait24(na, nb, nc);
+        // ---- the window's four rows are lanes 4g..4g+3: reduce-scatter the block's 18 sums -----------
+        // step 1 (lane bit 0): 9 each; step 2 (lane bit 1): 5 / 4 (+ one empty slot)
+        float w9[9];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) { ra[e] = na[e]; rb[e] = nb[e]; rc[e] = nc[e]; }
+        for (int i = 0; i < 9; ++i) {
+          const float send = b0 ? z[i] : z[i + 9];
+          const float keep = b0 ? z[i + 9] : z[i];
+          w9[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
         }
-      }
-
-      // ---- the window's four rows are lanes 4g..4g+3: reduce-scatter, 9 of the 36 sums per lane ----
-      const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
-      float w18[18];
+        float u[5];
 #pragma unroll
-      for (int i = 0; i < 18; ++i) {
-        const float send = b0 ? z[i] : z[i + 18];
-        const float keep = b0 ? z[i + 18] : z[i];
-        w18[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
-      }
-      float u[9];
+        for (int i = 0; i < 5; ++i) {
+          const float hi9 = (i < 4) ? w9[i + 5] : 0.f;
+          const float send = b1 ? w9[i] : hi9;
+          const float keep = b1 ? hi9 : w9[i];
+          u[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        }
+        // this lane holds the sums e = e0 .. e0+4 of the block (e = 6 * window column + map); for lanes
+        // with bit 1 set the fifth slot is empty
+        const int e0 = (b0 ? 9 : 0) + (b1 ? 5 : 0);
+        const float* wrow = &sm.wf[pw][18 * xb + e0][0];
 #pragma unroll
-      for (int i = 0; i < 9; ++i) {
-        const float send = b1 ? w18[i] : w18[i + 9];
-        const float keep = b1 ? w18[i + 9] : w18[i];
-        u[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-      }
-      const int idx0 = (b0 ? 18 : 0) + (b1 ? 9 : 0);   // this lane holds sums 6 * q + f = idx0 .. idx0 + 8
-      // ---- subsample sigmoid and this lane's share of the FC -----------------------------------------
-      float fc[kOut];
-#pragma unroll
-      for (int kk = 0; kk < kOut; ++kk) fc[kk] = 0.f;
-      const float* wrow = &sm.wf[p < 6 ? p : 6][idx0][0];
-#pragma unroll
-      for (int i = 0; i < 9; ++i) {
-        const float zs = u[i] + bs_eff;
-        const float as = kPrecise ? sigmoidf<SIG>(zs) : fmaf(0.5f, tanh_approx(0.5f * zs), 0.5f);
-        const float4 w0 = *reinterpret_cast<const float4*>(wrow + i * 12);
-        const float4 w1 = *reinterpret_cast<const float4*>(wrow + i * 12 + 4);
-        const float2 w2 = *reinterpret_cast<const float2*>(wrow + i * 12 + 8);
-        fc[0] = fmaf(w0.x, as, fc[0]); fc[1] = fmaf(w0.y, as, fc[1]); fc[2] = fmaf(w0.z, as, fc[2]);
-        fc[3] = fmaf(w0.w, as, fc[3]); fc[4] = fmaf(w1.x, as, fc[4]); fc[5] = fmaf(w1.y, as, fc[5]);
-        fc[6] = fmaf(w1.z, as, fc[6]); fc[7] = fmaf(w1.w, as, fc[7]); fc[8] = fmaf(w2.x, as, fc[8]);
-        fc[9] = fmaf(w2.y, as, fc[9]);
+        for (int i = 0; i < 5; ++i) {
+          const float zs = u[i] + bs_eff;
+          float as = kPrecise ? sigmoidf<SIG>(zs) : fmaf(0.5f, tanh_approx(0.5f * zs), 0.5f);
+          if (i == 4 && b1) as = 0.f;
+          const float4 w0 = *reinterpret_cast<const float4*>(wrow + i * 12);
+          const float4 w1 = *reinterpret_cast<const float4*>(wrow + i * 12 + 4);
+          const float2 w2 = *reinterpret_cast<const float2*>(wrow + i * 12 + 8);
+          fc[0] = fmaf(w0.x, as, fc[0]); fc[1] = fmaf(w0.y, as, fc[1]); fc[2] = fmaf(w0.z, as, fc[2]);
+          fc[3] = fmaf(w0.w, as, fc[3]); fc[4] = fmaf(w1.x, as, fc[4]); fc[5] = fmaf(w1.y, as, fc[5]);
+          fc[6] = fmaf(w1.z, as, fc[6]); fc[7] = fmaf(w1.w, as, fc[7]); fc[8] = fmaf(w2.x, as, fc[8]);
+          fc[9] = fmaf(w2.y, as, fc[9]);
+        }
       }
 #pragma unroll
       for (int kk = 0; kk < kOut; ++kk) {

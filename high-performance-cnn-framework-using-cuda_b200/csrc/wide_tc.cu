@@ -6,7 +6,7 @@
 //   1. every thread gathers the 25 taps of its row straight from the image (L1/L2-resident) and
 //      writes them, split into a tf32-exact high part and the remainder, into the two A tiles in
 //      shared memory in the canonical un-swizzled K-major layout;
-//   2. one thread issues 4 (one pass) or 12 (three passes: hi*hi + lo*hi + hi*lo, fp32-level
+//   2. one elected lane of warp 0 issues 4 (one pass) or 12 (three passes: hi*hi + lo*hi + hi*lo, fp32-level
 //      accuracy) tcgen05.mma of shape 128 x F x 8 with the accumulator in tensor memory, and commits
 //      to an mbarrier;
 //   3. after the (bounded) wait each warp reads its 32 accumulator lanes back with tcgen05.ld, adds
@@ -108,7 +108,7 @@ k_wide_conv_fwd_tc(WideDims d, const float* __restrict__ images, long n, const f
     tc::fence_before_sync();    // this thread's TMEM loads of the previous tile are complete
     __syncthreads();
     // ---- 2. MMAs ----------------------------------------------------------------------------------
-    if (tid == 0) {
+    if (warp == 0) {   // the whole warp runs the loop, an elected lane issues (see wide_tc.cuh)
       tc::fence_after_sync();
       unsigned accumulate = 0;
       for (int pass = 0; pass < passes; ++pass) {
@@ -118,11 +118,11 @@ k_wide_conv_fwd_tc(WideDims d, const float* __restrict__ images, long n, const f
         for (int ks = 0; ks < 4; ++ks) {    // K = 8 per MMA = two 16-byte chunks
           const unsigned long long ad = tc::smem_desc(a_s + ks * 256, 128, group);
           const unsigned long long bd = tc::smem_desc(b_s + ks * 256, 128, group);
-          tc::mma_tf32(tmem_d, ad, bd, idesc, accumulate);
+          tc::mma_tf32_elect(tmem_d, ad, bd, idesc, accumulate);
           accumulate = 1;
         }
       }
-      tc::mma_commit(bar);
+      tc::mma_commit_elect(bar);
     }
     mbar_wait_bounded(bar, phase, status, gave_up);
     phase ^= 1u;
@@ -292,7 +292,7 @@ k_wide_grad_c1_tc(WideDims d, const float* __restrict__ images, const float* __r
     }
     tc::fence_async_smem();
     __syncthreads();
-    if (tid == 0) {
+    if (warp == 0) {   // the whole warp runs the loop, an elected lane issues (see wide_tc.cuh)
       tc::fence_after_sync();
       for (int pass = 0; pass < passes; ++pass) {
         const unsigned a_s = (pass == 1) ? a_lo_s : a_hi_s;
@@ -301,11 +301,11 @@ k_wide_grad_c1_tc(WideDims d, const float* __restrict__ images, const float* __r
         for (int ks = 0; ks < kTcRows / 8; ++ks) {   // 8 positions per MMA
           const unsigned long long ad = tc::smem_desc(a_s + ks * 256, 128, a_group);
           const unsigned long long bd = tc::smem_desc(b_s + ks * 256, 128, a_group);
-          tc::mma_tf32(tmem_d, ad, bd, idesc, accumulate);
+          tc::mma_tf32_elect(tmem_d, ad, bd, idesc, accumulate);
           accumulate = 1;
         }
       }
-      tc::mma_commit(bar);
+      tc::mma_commit_elect(bar);
     }
     mbar_wait_bounded(bar, phase, status, gave_up);   // the tiles may be overwritten
     phase ^= 1u;

@@ -62,6 +62,27 @@ __device__ __forceinline__ void mma_tf32(unsigned tmem_d, unsigned long long ade
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same, called by a WHOLE converged warp: the operands are warp-uniform and one elected lane
+// issues.  Measured on B200: a tcgen05.mma issued from inside a divergent branch ("if (tid == 0)")
+// costs the issuing thread about 146 cycles whatever its shape; issued this way a 128 x 80 x 8 tf32
+// MMA costs 58 cycles, which is its operand traffic (6.5 KB of shared memory at 128 B/cycle).
+__device__ __forceinline__ void mma_tf32_elect(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                               unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Whole converged warp: the lane that elect.sync picks (the same one every time for a full mask)
+// arrives on the mbarrier when every MMA it has issued so far has completed.
+__device__ __forceinline__ void mma_commit_elect(unsigned long long* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
+      : "memory");
+}
 // Arrive on an mbarrier when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

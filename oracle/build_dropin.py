@@ -16,7 +16,10 @@ import tempfile
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 REF_DIR = os.path.join(HERE, "_ref")
-REFERENCE_CHECKOUT = os.environ.get("CNN_REFERENCE_DIR", "/root/reference")
+# The reference checkout: $CNN_REFERENCE_DIR, else a directory "reference" beside the repository.
+# Where neither exists the prebuilt files under _ref/ are used as they are.
+REFERENCE_CHECKOUT = os.environ.get(
+    "CNN_REFERENCE_DIR", os.path.normpath(os.path.join(HERE, "..", "..", "reference")))
 COMPAT = os.path.join(ROOT, "high-performance-cnn-framework-using-cuda_b200", "compat")
 TARGETS = {"reference": os.path.join(REF_DIR, "CNN_reference.exe"), "dropin": os.path.join(REF_DIR, "CNN_dropin.exe")}
 

@@ -17,7 +17,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle_cnn.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libref_cnn.so")
-REFERENCE_CHECKOUT = os.environ.get("CNN_REFERENCE_DIR", "/root/reference")
+# The reference checkout: $CNN_REFERENCE_DIR, else a directory "reference" beside the repository.
+# Where neither exists the prebuilt files under _ref/ are used as they are.
+REFERENCE_CHECKOUT = os.environ.get(
+    "CNN_REFERENCE_DIR", os.path.normpath(os.path.join(HERE, "..", "..", "reference")))
 
 
 def _newer(target: str, sources: list[str]) -> bool:
