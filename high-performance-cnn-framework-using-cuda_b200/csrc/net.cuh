@@ -42,6 +42,10 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
+// One arrival on an mbarrier of this CTA (release at CTA scope).
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 // 1-D bulk copy global -> this CTA's shared memory, completion signalled on an mbarrier.
 // Both addresses must be 16-byte aligned and bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes,

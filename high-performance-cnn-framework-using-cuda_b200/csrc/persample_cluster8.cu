@@ -356,18 +356,23 @@ k_train_persample_cluster8(const float* __restrict__ images, const unsigned* __r
         const float mine = warp_reduce_scatter32(g, lane);
         if (lane < 26) sm.c_part[warp][lane] = mine;
       }
+      // (the service warp is the last to leave the stretch between B2 and E: what it can read or
+      // compute before B2 it does here, while it waits for the compute warps anyway)
+      float w_old = 0.f, bf_new = 0.f;
+      if (service) {
+        w_old = (lane < 25) ? sm.wc[lane] : sm.bc[0];
+        if (lane < kOut) bf_new = fmaf(dt, delta, sm.bf[lane]);          // bp_bias_f, stored after B2: a compute
+      }                                                                  // warp may still be reading bf before it
       CNN_PHASE(7);     // at barrier B2 (compute: reduce-scatter done; service: error norm done)
       __syncthreads();  // (B2)
 
       if (service) {
         if (lane < 26) {
-          float sum = 0.f;
-#pragma unroll
-          for (int ww = 0; ww < kC8Compute; ++ww) sum += sm.c_part[ww][lane];
-          if (lane < 25) sm.wc[lane] = fmaf(dt, sum, sm.wc[lane]);       // apply_grad (c1)
-          else sm.bc[0] = fmaf(dt, sum, sm.bc[0]);                       // bp_bias_c1
+          const float sum = (sm.c_part[0][lane] + sm.c_part[1][lane]) + sm.c_part[2][lane];
+          if (lane < 25) sm.wc[lane] = fmaf(dt, sum, w_old);             // apply_grad (c1)
+          else sm.bc[0] = fmaf(dt, sum, w_old);                          // bp_bias_c1
         }
-        if (lane < kOut) sm.bf[lane] = fmaf(dt, delta, sm.bf[lane]);     // bp_bias_f
+        if (lane < kOut) sm.bf[lane] = bf_new;
       } else if (warp == 0 && lane < 17) {
         float sum = 0.f;
 #pragma unroll
