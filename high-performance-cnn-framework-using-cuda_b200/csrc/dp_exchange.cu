@@ -31,7 +31,7 @@ namespace cnn {
 
 constexpr int kDpMaxRanks = 8;
 constexpr int kDpBlocks = (kNParamsPadded + 31) / 32;   // 74 blocks of 32 columns
-constexpr int kDpRedGroups = 8;
+constexpr int kDpRedGroups = 16;   // row groups per column: 512 threads per block, at most ~19 dependent adds per thread
 
 // Exchange buffer of one rank (device memory of that rank; every rank maps all of them).
 struct DpBuffer {
@@ -89,8 +89,23 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
   }
   const unsigned seq = mine->step[b] + 1u;      // written only by this block, one launch ago
   const int parity = (int)(seq & 1u);
-  const float total = ((part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane])) +
-                      ((part[4][lane] + part[5][lane]) + (part[6][lane] + part[7][lane]));
+  float total;
+  {
+    float q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      q[i] = (part[4 * i][lane] + part[4 * i + 1][lane]) + (part[4 * i + 2][lane] + part[4 * i + 3][lane]);
+    total = (q[0] + q[1]) + (q[2] + q[3]);
+  }
+  if (world == 1) {
+    // a single rank has nobody to exchange with: reduce + update, no flags, no system-scope fences
+    if (col < kRowStride) {
+      if (G) G[col] = total;
+      if (col < kNParams) params[col] = fmaf(scale, total, params[col]);
+      if (mean_err && col == kRowErr) *mean_err += err_scale * total;
+    }
+    return;
+  }
   if (send) {
     if (col < kRowStride) {
 #pragma unroll

@@ -304,10 +304,11 @@ k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ l
   if (tid < kRowStride - kNParams && kNParams + tid != kRowErr) row[kNParams + tid] = 0.f;
 }
 
-// G[i] = sum over rows (fixed order: eight interleaved row groups, then a fixed tree over the
+// G[i] = sum over rows (fixed order: sixteen interleaved row groups, then a fixed tree over the
 // groups) and, if params is given, params[i] += scale * G[i].  Element kRowErr carries the error sum;
-// if mean_err is given, *mean_err += err_scale * that sum.  Block: 256 threads = 32 columns x 8 groups.
-constexpr int kRedGroups = 8;
+// if mean_err is given, *mean_err += err_scale * that sum.  Block: 512 threads = 32 columns x 16 groups.
+// (The data-parallel exchange kernel adds a rank's rows in exactly this order.)
+constexpr int kRedGroups = 16;
 
 __global__ void __launch_bounds__(32 * kRedGroups)
 k_reduce_rows(const float* __restrict__ rows, int n_rows, float* __restrict__ G,
@@ -323,8 +324,11 @@ k_reduce_rows(const float* __restrict__ rows, int n_rows, float* __restrict__ G,
   part[g][lane] = acc;
   __syncthreads();
   if (g == 0 && col < kRowStride) {
-    const float total = ((part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane])) +
-                        ((part[4][lane] + part[5][lane]) + (part[6][lane] + part[7][lane]));
+    float q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      q[i] = (part[4 * i][lane] + part[4 * i + 1][lane]) + (part[4 * i + 2][lane] + part[4 * i + 3][lane]);
+    const float total = (q[0] + q[1]) + (q[2] + q[3]);
     if (G) G[col] = total;
     if (params && col < kNParams) params[col] = fmaf(scale, total, params[col]);
     if (mean_err && col == kRowErr) *mean_err += err_scale * total;
@@ -512,11 +516,14 @@ int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_
   return CNN_OK;
 }
 
-// Small batches: one block per SM (latency).  From 8 images per SM on: two blocks per SM (throughput).
+// Blocks of the gradient kernel.  Up to two blocks per SM there is one image per block (a training
+// step of a few hundred images is pure latency: one image per block halves it against two images
+// in sequence on half as many blocks); from 8 images per SM on, two blocks per SM walk the batch.
 int grid_for_batch(long n) {
   const long sms = sm_count();
+  if (n <= 2 * sms) return (int)n;
   const long cap = (n >= 8 * sms) ? 2 * sms : sms;
-  return (int)(n < cap ? n : cap);
+  return (int)cap;
 }
 
 }  // namespace cnn
