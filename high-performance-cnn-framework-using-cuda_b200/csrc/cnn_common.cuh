@@ -41,12 +41,15 @@ __device__ __forceinline__ float exp2f_approx(float x) {
 
 // step_function, layer.cu:81-84.  Three flavours, selected at compile time:
 //   0  the reference's own expression, compiled without fast-math (libdevice expf, IEEE divide):
-//      equal pre-activations give bit-equal activations;
-//   1  __expf and __fdividef (ex2.approx / rcp.approx based): about 1e-6 relative from flavour 0
-//      for |v| <= 16 (the multiplication by log2e is rounded before the exponential);
-//   2  same two special-function instructions, but with the argument reduced in two FMA steps
-//      (n = round(-v*log2e), r = -v - n*ln2 exactly) and one Newton step on the reciprocal:
-//      about 12 instructions, within a few 1e-7 relative of flavour 0 per evaluation (the default).
+//      equal pre-activations give bit-equal activations; about 21 instructions;
+//   1  the short form, __expf and __fdividef (ex2.approx / rcp.approx, four dependent instructions):
+//      about 1e-6 relative from flavour 0 per evaluation for |v| <= 16 (the multiplication by log2e is
+//      rounded before the exponential).  What the fused kernels of the 28x28 net use when
+//      fast_sigmoid is set: on the network's outputs it is as close to the fp64 oracle as flavour 0
+//      (2.1e-6 over 65,536 images);
+//   2  the same two special-function instructions with the argument reduced in two FMA steps
+//      (n = round(-v*log2e), r = -v - n*ln2 exactly) and one Newton step on the reciprocal: about 12
+//      instructions, a few 1e-7 from flavour 0 per evaluation (selectable for the widened net).
 template <int FLAVOR>
 __device__ __forceinline__ float sigmoidf(float v) {
   if constexpr (FLAVOR == 1) {

@@ -26,8 +26,9 @@
 //
 // Pipeline (one CTA per SM, 16 warps, everything handed over through mbarriers with bounded waits):
 //   warps 2-3   load 136 stacked rows per tile straight into the operand layout with 16-byte
-//               cp.async copies (four slabs, two tiles of look-ahead); path 1 then splits its own
-//               chunks in place into the high and the low slab;
+//               cp.async copies (contiguous on the global side; eight slabs: path 2 keeps six tiles
+//               in flight, path 1 uses them as four (high, low) pairs and splits its own chunks in
+//               place after they land);
 //   warp 1      issues the tile's MMAs into one of three 160-column accumulators and commits to
 //               mbarriers (the whole warp runs the loop, an elected lane issues: see wide_tc.cuh);
 //   warps 4-15  three epilogue groups of four warps (one per 32-lane quarter of tensor memory), one
@@ -37,6 +38,9 @@
 //               window row's share of the FC into shared memory, counted on the image's mbarrier;
 //   warp 0      finishes images in order, three at a time: adds the six window rows' FC sums, output
 //               sigmoid, argmax (lowest index wins ties), 44 bytes per image to HBM.
+// Measured on a B200, 65,536 images: path 2 0.131 ms (5.0e8 images/s; the special-function unit -- one
+// tanh per conv output -- and shared-memory bandwidth bound it), path 1 0.46 ms (three passes' operand
+// traffic plus 3,682 exact sigmoids per image: no faster than the fp32 SIMT kernel's 0.39 ms).
 #include "net.cuh"
 #include "wide_tc.cuh"
 

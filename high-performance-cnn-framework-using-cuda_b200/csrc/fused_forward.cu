@@ -219,18 +219,19 @@ static int launch_variant(cnn_net* net, const void* d_images, long n, float* d_o
   return CNN_OK;
 }
 
-// With the default sigmoid the loop over the six maps is unrolled by two (more independent sigmoid
-// chains in flight at the same 96 registers); three-fold unrolling spills.
+// fast_sigmoid set (the default): the short sigmoid form, 0.387 ms per 65,536 images against 0.447 ms
+// for the refined form (map loop unrolled by two) and 0.546 ms for the reference expression; over that
+// batch all three are equally close to the fp64 oracle (2.1e-6; the fp32 oracle itself is 4.0e-6 away).
 int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                    cudaStream_t stream) {
   if (net->forward_path != 0) return forward_device_tc(net, d_images, n, d_out, d_argmax, stream);
-  return net->fast_sigmoid ? launch_variant<2, false, 2>(net, d_images, n, d_out, d_argmax, stream)
+  return net->fast_sigmoid ? launch_variant<1, false, 1>(net, d_images, n, d_out, d_argmax, stream)
                            : launch_variant<0, false, 1>(net, d_images, n, d_out, d_argmax, stream);
 }
 
 int forward_device_u8(cnn_net* net, const unsigned char* d_pixels, long n, float* d_out, int* d_argmax,
                       cudaStream_t stream) {
-  return net->fast_sigmoid ? launch_variant<2, true, 2>(net, d_pixels, n, d_out, d_argmax, stream)
+  return net->fast_sigmoid ? launch_variant<1, true, 1>(net, d_pixels, n, d_out, d_argmax, stream)
                            : launch_variant<0, true, 1>(net, d_pixels, n, d_out, d_argmax, stream);
 }
 

@@ -508,7 +508,7 @@ int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_
                                                              net->d_partials, net->d_status);      \
     }                                                                                              \
   } while (0)
-  if (net->fast_sigmoid) CNN_LAUNCH_GRAD(2);
+  if (net->fast_sigmoid) CNN_LAUNCH_GRAD(1);
   else CNN_LAUNCH_GRAD(0);
 #undef CNN_LAUNCH_GRAD
   cudaError_t e = cudaGetLastError();
@@ -619,7 +619,7 @@ int cnn_train_sgd_persample(cnn_net* net, const float* d_images, const unsigned 
     k_train_persample<FL><<<1, kTrThreads, smem, st>>>(d_images, d_labels, n, epochs, dt, threshold, \
                                                        net->d_params, d_mean, d_ran, net->d_status); \
   } while (0)
-  if (net->fast_sigmoid) CNN_LAUNCH_PS(2);
+  if (net->fast_sigmoid) CNN_LAUNCH_PS(1);
   else CNN_LAUNCH_PS(0);
 #undef CNN_LAUNCH_PS
   }

@@ -128,7 +128,7 @@ int cnn_net_params_device(cnn_net* net, float** d_params) {
 
 int cnn_net_set_fast_sigmoid(cnn_net* net, int enable) {
   CNN_REQUIRE(net, "cnn_net_set_fast_sigmoid: NULL net");
-  net->fast_sigmoid = enable ? 2 : 0;
+  net->fast_sigmoid = enable ? 1 : 0;
   return CNN_OK;
 }
 
@@ -145,7 +145,7 @@ int cnn_net_set_option(cnn_net* net, const char* key, int value) {
     return CNN_OK;
   }
   if (std::strcmp(key, "fast_sigmoid") == 0) {
-    net->fast_sigmoid = value ? 2 : 0;
+    net->fast_sigmoid = value ? 1 : 0;
     return CNN_OK;
   }
   set_error("cnn_net_set_option: unknown option '%s'", key);

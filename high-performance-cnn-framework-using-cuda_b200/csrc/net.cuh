@@ -11,7 +11,7 @@ struct cnn_net {
                                    // tf32 passes (fp32-level accuracy), 2 = tensor cores, one tf32 pass + tanh sigmoid
   float* d_params = nullptr;       // kNParamsPadded floats
   int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out
-  int fast_sigmoid = 2;            // sigmoid flavour of the fused kernels: 0 (reference expression) or 2 (default)
+  int fast_sigmoid = 1;            // sigmoid of the fused kernels: 0 = reference expression, 1 = short form (default)
 
   // Training scratch (allocated on first use): per-block partial gradients and the reduced vector.
   float* d_partials = nullptr;     // [partial_rows][kNParamsPadded]

@@ -34,15 +34,11 @@ namespace cg = cooperative_groups;
 
 namespace cnn {
 
-// Sigmoid behind fast_sigmoid != 0.  This kernel is a chain of dependent latencies (three sigmoids in
-// sequence per sample), so it takes the short form -- ex2.approx and rcp.approx, four dependent
-// instructions, about 1e-6 relative per evaluation -- instead of the refined twelve-instruction one
-// of the throughput kernels: measured 1.646 against 1.714 us per sample, with the same distance from
-// the oracle after 2,000 steps (1.2e-5 of the largest parameter, set by summation order).
-#ifndef CNN_PS_FAST_FLAVOR
-#define CNN_PS_FAST_FLAVOR 1
-#endif
-constexpr int kC8FastFlavor = CNN_PS_FAST_FLAVOR;
+// Sigmoid behind fast_sigmoid != 0: the short form (cnn_common.cuh).  This kernel is a chain of
+// dependent latencies with three sigmoids in sequence per sample: 1.646 us per sample with it against
+// 1.714 us with the refined twelve-instruction form, and the same distance from the oracle after 2,000
+// steps (1.2e-5 of the largest parameter, set by summation order).
+constexpr int kC8FastFlavor = 1;
 constexpr int kC8Threads = 128;
 constexpr int kC8Compute = 3;                 // compute warps
 constexpr int kC8WinPerWarp = 12;

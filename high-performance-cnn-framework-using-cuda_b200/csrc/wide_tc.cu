@@ -225,6 +225,12 @@ k_wide_grad_c1_tc(WideDims d, const float* __restrict__ images, const float* __r
 
   bool gave_up = false;
   unsigned phase = 0, accumulate = 0;
+  constexpr int kWgFlush = 2;
+  int since_flush = 0;
+  float racc[32];
+#pragma unroll
+  for (int c = 0; c < 32; ++c) racc[c] = 0.f;
+  const unsigned lane_base = tmem_d + ((unsigned)((warp & 3) * 32) << 16);
   for (long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const long m0 = tile * kTcRows;
     // ---- dcT tile: rows = maps, 32 chunks of 4 positions.  A warp-wide step covers 8 maps x 4
@@ -309,6 +315,25 @@ k_wide_grad_c1_tc(WideDims d, const float* __restrict__ images, const float* __r
     }
     mbar_wait_bounded(bar, phase, status, gave_up);   // the tiles may be overwritten
     phase ^= 1u;
+    // Every kWgFlush tiles the accumulator moves into registers and starts again from zero: the tensor
+    // core adds into its fp32 accumulator with truncation, about one ulp of the running sum per MMA, and
+    // 48 MMAs per tile over the ~18 tiles of a CTA at batch 1,024 left the conv-filter gradient 5e-5
+    // from the fp64 oracle.  Two tiles per flush keep it at 1e-6; the sums below round to nearest.
+    if (++since_flush == kWgFlush) {
+      since_flush = 0;
+      accumulate = 0;
+      tc::fence_after_sync();
+      if (warp < 4) {
+#pragma unroll
+        for (int c0 = 0; c0 < 32; c0 += 16) {
+          float acc[16];
+          tc::tmem_ld16(lane_base + (unsigned)c0, acc);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) racc[c0 + e] += acc[e];
+        }
+      }
+      tc::fence_before_sync();   // ordered before the next tile's MMAs by the block barrier that precedes them
+    }
   }
   tc::fence_after_sync();
   // ---- epilogue: M = 128: lane l of warp w is map 32w + l; M = 64: lanes 0..15 are maps 16w + l ----
@@ -316,17 +341,15 @@ k_wide_grad_c1_tc(WideDims d, const float* __restrict__ images, const float* __r
     const bool full = d.F == 128;
     const int f = full ? (32 * warp + lane) : (16 * warp + lane);
     const bool owner = full || lane < 16;
-    const unsigned lane_base = tmem_d + ((unsigned)(warp * 32) << 16);
     float* dst = part + ((size_t)blockIdx.x * d.F + (owner ? f : 0)) * 26;
-    const bool any = blockIdx.x < n_tiles;   // a CTA without tiles never wrote its accumulator
 #pragma unroll
     for (int c0 = 0; c0 < 32; c0 += 16) {
       float acc[16];
-      tc::tmem_ld16(lane_base + (unsigned)c0, acc);
+      if (since_flush != 0) tc::tmem_ld16(lane_base + (unsigned)c0, acc);   // what has not been flushed yet
       if (owner) {
 #pragma unroll
         for (int e = 0; e < 16; ++e)
-          if (c0 + e < 26) dst[c0 + e] = any ? acc[e] : 0.f;
+          if (c0 + e < 26) dst[c0 + e] = racc[c0 + e] + (since_flush != 0 ? acc[e] : 0.f);
       }
     }
   }

@@ -129,13 +129,14 @@ int cnn_net_get_params(cnn_net* net, float* h_params);
 /* Device pointer of the arena (CNN_N_PARAMS floats, padded to 2368), for collectives. */
 int cnn_net_params_device(cnn_net* net, float** d_params);
 
-/* Sigmoid flavour of the fused kernels (the per-operator kernels always use the reference's):
+/* Sigmoid of the fused kernels (the per-operator kernels always use the reference's expression):
  *   0 = the reference's own expression 1/(1+expf(-v)) with IEEE division (layer.cu:81-84): equal
  *       pre-activations give bit-equal activations, about 21 instructions per evaluation;
- *   non-zero (default) = two-step argument reduction, ex2.approx and a Newton-refined reciprocal: the
- *       same special-function instruction expf itself is built on; per evaluation a few 1e-7 relative
- *       from flavour 0, on the network's outputs at most 2.0e-6 over 65,536 images
- *       (tests/test_gpu_forward.py::test_sigmoid_flavours_agree measures it), 12 instructions.
+ *   non-zero (default) = the short form, ex2.approx and rcp.approx (the special-function instructions
+ *       expf and the division are themselves built on), four instructions, about 1e-6 relative per
+ *       evaluation.  On the network's outputs the two are equally close to an fp64 evaluation: 2.1e-6
+ *       over the 65,536 images of benchmark configuration 2, where the fp32 oracle itself is 4.0e-6 away
+ *       (tests/test_gpu_forward.py prints both).
  * Both meet the 1e-5 parity bar in every test. */
 int cnn_net_set_fast_sigmoid(cnn_net* net, int enable);
 

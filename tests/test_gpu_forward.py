@@ -39,7 +39,7 @@ def check_argmax(arg, ref_arg, ref_out, what, tol=1e-5, max_masked_frac=1e-3):
     assert masked <= max(1, int(max_masked_frac * len(arg)))
 
 
-@pytest.mark.parametrize("fast", [0, 2])
+@pytest.mark.parametrize("fast", [0, 1])
 @pytest.mark.parametrize("n", [1, 7, 8, 9, 100, 2368 + 5, 4099])
 def test_forward_matches_oracle(cuda, pkg, ob, params0, n, fast):
     images, _ = pkg.synth.synth_images(21, n)
@@ -54,7 +54,7 @@ def test_forward_matches_oracle(cuda, pkg, ob, params0, n, fast):
     assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
 
 
-@pytest.mark.parametrize("fast", [0, 2])
+@pytest.mark.parametrize("fast", [0, 1])
 def test_full_size_forward_matches_oracle(cuda, pkg, ob, params0, fast):
     """Benchmark configuration 2 at its full size: 65,536 images of seed 1 against the oracle --
     every sigmoid within 1e-5 relative, argmax equal on every clear-margin row; the number of rows
@@ -208,26 +208,29 @@ def test_uint8_input_is_bit_identical_to_fp32(cuda, pkg, params0, n):
     assert np.array_equal(h_out, out_f) and np.array_equal(h_arg, arg_f)
 
 
-def test_sigmoid_flavours_agree(cuda, pkg, params0):
-    """The default sigmoid against the reference expression (flavour 0) on the full benchmark batch:
-    maximum relative difference of the ten outputs."""
+def test_sigmoid_flavours_agree(cuda, pkg, ob, params0):
+    """The default (short) sigmoid form against the reference expression on the full benchmark batch:
+    maximum relative difference of the ten outputs between the two, and the distance of each from the
+    fp64 oracle, beside the fp32 oracle's own distance from it."""
     n = 65536
-    d_img = cuda.empty((n, 28, 28), dtype=cuda.float32, device="cuda")
-    pkg.synth_images_device(1, 0, n, d_img)
+    images, _ = pkg.synth.synth_images(1, n)
+    d_img = cuda.from_numpy(images).cuda()
+    ref64, _ = ob.forward_batch(params0, images, threads=0, dtype=np.float64)
+    ref32, _ = ob.forward_batch(params0, images, threads=0)
     outs = {}
-    for fl in (0, 2):
+    for fl in (0, 1):
         net = pkg.Net(0)
         net.set_params(params0)
         net.set_fast_sigmoid(fl)
         o = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
         net.forward(d_img, n, o, None)
         cuda.cuda.synchronize()
-        outs[fl] = o.double()
-    d2 = float(((outs[2] - outs[0]).abs() / outs[0]).max())
-    print("max relative difference to the reference expression: %.3e" % d2)
-    # each evaluation is within a few 1e-7 of the exact sigmoid (so is libdevice's expf); three
-    # layers deep the outputs differ by up to ~2e-6 in the tails
-    assert d2 < 5e-6
+        outs[fl] = o.cpu().numpy().astype(np.float64)
+    d = float(np.max(np.abs(outs[1] - outs[0]) / outs[0]))
+    e0, e1, eo = rel_err(outs[0], ref64), rel_err(outs[1], ref64), rel_err(ref32, ref64)
+    print("short form vs reference expression: %.3e; against the fp64 oracle: reference expression %.3e, "
+          "short form %.3e, fp32 oracle %.3e" % (d, e0, e1, eo))
+    assert d < 5e-6 and e1 < max(5e-6, 1.5 * e0)
 
 
 def test_forward_host_is_ordered_behind_legacy_stream_work(cuda, pkg, params0):
@@ -255,7 +258,7 @@ def test_forward_host_is_ordered_behind_legacy_stream_work(cuda, pkg, params0):
 
 
 # ---- the convolution on the tensor cores (option "forward_path") ------------------------------------
-@pytest.mark.parametrize("fast", [0, 2])
+@pytest.mark.parametrize("fast", [0, 1])
 @pytest.mark.parametrize("n", [1, 5, 16, 17, 100, 2368 + 5, 4099])
 def test_tensor_core_forward_three_passes_matches_oracle(cuda, pkg, ob, params0, n, fast):
     """forward_path = 1: tcgen05 convolution in three tf32 passes keeps the 1e-5 bar of the fp32 path."""

@@ -42,7 +42,7 @@ def gpu_grad(torch, net, images, labels):
     return d_g.cpu().numpy()
 
 
-@pytest.mark.parametrize("fast", [0, 2])
+@pytest.mark.parametrize("fast", [0, 1])
 @pytest.mark.parametrize("n", [1, 2, 147, 148, 149, 256, 1000])
 def test_grad_batch_matches_oracle(cuda, pkg, ob, params0, n, fast):
     images, labels = pkg.synth.synth_images(31, n)
@@ -110,7 +110,7 @@ def test_single_sgd_step_matches_oracle_and_reference(cuda, pkg, ob, params0, da
         ref.close()
 
 
-@pytest.mark.parametrize("fast", [0, 2])
+@pytest.mark.parametrize("fast", [0, 1])
 def test_persample_trajectory_matches_oracle(cuda, pkg, ob, params0, fast):
     """2,000 sequential SGD steps (two epochs of 1,000).  Rounding differences compound along the
     chain, so the bar on parameters is 1e-3 of the largest parameter here, with 1e-5 kept for the
@@ -170,7 +170,7 @@ def test_persample_kernels_single_step_matches_oracle(cuda, pkg, ob, params0, ke
     assert np.allclose(mean_err, m_or, rtol=1e-5)
 
 
-@pytest.mark.parametrize("fast", [0, 2])
+@pytest.mark.parametrize("fast", [0, 1])
 def test_persample_cluster_kernel_against_single_block(cuda, pkg, ob, params0, fast):
     """The cluster kernel adds the same terms in another order than the single-block kernel: over 3
     epochs of 700 samples both stay within the trajectory bar of the oracle and of each other, stop
