@@ -489,7 +489,18 @@ def run_ours(args):
         pnet.forward(d_img1[CONFIG1_TRAIN:], CONFIG1_TEST, None, d_arg1, stream)
         torch.cuda.synchronize()
         acc = float((d_arg1 == d_lab1[CONFIG1_TRAIN:]).float().mean().item())
-        return {"what": "benchmark configuration 1: per-sample SGD in file order over 10,000 images (one persistent cluster of "
+        phases = pkg.persample_phase_clocks()      # None unless the library was built with CNN_PHASE_CLOCKS
+        if phases is not None:
+            rel = phases / CONFIG1_TRAIN
+            rel = rel - rel[0, 0]
+            extra_phase = {"phase_clocks": {"note": "mean SM clock of each warp of CTA 0 at each stamp, cycles after warp 0 "
+                                                     "reaches the top of the loop; the stamps slow the kernel down",
+                                            "stamps": list(pkg.PHASE_CLOCK_STAMPS),
+                                            "warps": [[round(float(v), 1) for v in rel[w, :len(pkg.PHASE_CLOCK_STAMPS)]]
+                                                      for w in range(4)]}}
+        else:
+            extra_phase = {}
+        return {**extra_phase, "what": "benchmark configuration 1: per-sample SGD in file order over 10,000 images (one persistent cluster of "
                         "six CTAs; does not shard), then argmax over 2,000 test images; labels are uniform random, so "
                         "accuracy is chance level for every arm",
                 "train_images_per_s": CONFIG1_TRAIN / best, "us_per_sample": 1e6 * best / CONFIG1_TRAIN,

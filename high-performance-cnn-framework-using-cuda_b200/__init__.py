@@ -23,7 +23,8 @@ import numpy as np
 from . import checkpoint, synth  # noqa: F401  (re-exported)
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libcnn_b200.so")
+# CNN_B200_LIBRARY names an instrumented build of the same library (build.py --define ... --out ...).
+LIB_PATH = os.environ.get("CNN_B200_LIBRARY") or os.path.join(PKG_DIR, "libcnn_b200.so")
 HEADER_PATH = os.path.join(PKG_DIR, "..", "include", "cnn_b200.h")
 
 N_PARAMS = 2343
@@ -544,6 +545,26 @@ def grad_batch_noalloc_status(stream=None) -> None:
     """Waits for ``stream`` and raises ``CnnError`` (code -3) if a ``grad_batch_noalloc`` call on the
     current device gave up a bounded wait since the last query.  Allocates nothing."""
     _check(load_library().cnn_grad_batch_noalloc_status(_stream(stream)))
+
+
+PHASE_CLOCK_STAMPS = ("top of the loop", "convolution + 8 sigmoids", "at barrier A", "subsample + FC partials sent",
+                      "exchange landed", "output layer", "deltas + gradient terms", "at barrier B2", "at barrier E")
+
+
+def persample_phase_clocks():
+    """Per-warp sums of the SM clock at each stamp of the per-sample cluster kernel's loop, as a
+    float64 array [4 warps][16 stamps] (CTA 0; warps 0-2 compute, warp 3 service; see
+    PHASE_CLOCK_STAMPS), accumulated over the samples of the last run.  Only a library built with
+    ``build.py --define CNN_PHASE_CLOCKS`` exports it; returns None otherwise."""
+    lib = load_library()
+    try:
+        fn = lib.cnn_debug_phase_clocks8
+    except AttributeError:
+        return None
+    out = (C.c_longlong * 64)()
+    fn.restype = C.c_int
+    _check(fn(out))
+    return np.array(out[:], dtype=np.float64).reshape(4, 16)
 
 
 def synth_images_device(seed: int, first_index: int, n: int, d_images, d_labels=None, stream=None) -> None:

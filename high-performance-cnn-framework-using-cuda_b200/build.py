@@ -2,6 +2,11 @@
 
 Usage: ``python build.py [--force] [--verbose]`` or ``build_library()`` from Python.
 nvcc cross-compiles without a GPU; the resulting shared object sits next to this file.
+
+``python build.py --define NAME [--define NAME2 ...] --out PATH`` builds an instrumented copy of
+the library (for example ``--define CNN_PHASE_CLOCKS``, which compiles the per-sample kernel's
+clock stamps in) into PATH with its objects in a directory of their own; the package loads it when
+the environment variable CNN_B200_LIBRARY names it.
 """
 from __future__ import annotations
 
@@ -42,9 +47,9 @@ def _up_to_date() -> bool:
     return all(os.path.getmtime(d) <= t for d in _deps() if os.path.exists(d))
 
 
-def _compile(src: str, verbose: bool) -> tuple[str, str]:
-    obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
-    cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
+def _compile(src: str, verbose: bool, obj_dir: str = OBJ_DIR, defines: tuple[str, ...] = ()) -> tuple[str, str]:
+    obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
+    cmd = ["nvcc"] + NVCC_FLAGS + ["-D" + d for d in defines] + (["-Xptxas", "-v"] if verbose else []) + [
         "-c", os.path.join(CSRC, src), "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
@@ -52,27 +57,44 @@ def _compile(src: str, verbose: bool) -> tuple[str, str]:
     return obj, r.stderr
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Compile every CUDA source of the package for sm_100a; returns the library path."""
+def build_library(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (),
+                  out: str | None = None) -> str:
+    """Compile every CUDA source of the package for sm_100a; returns the library path.
+
+    With `defines` and `out` an instrumented copy is built into `out` (always from scratch)."""
+    if defines or out:
+        if not out:
+            raise ValueError("an instrumented build needs its own output path (out=...)")
+        return _build(verbose, tuple(defines), os.path.abspath(out), os.path.abspath(out) + ".objs")
     if not force and _up_to_date():
         return LIB_PATH
     if shutil.which("nvcc") is None:
         if os.path.exists(LIB_PATH):
             return LIB_PATH
         raise RuntimeError("nvcc not found and no prebuilt libcnn_b200.so present")
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    return _build(verbose, (), LIB_PATH, OBJ_DIR)
+
+
+def _build(verbose: bool, defines: tuple[str, ...], lib_path: str, obj_dir: str) -> str:
+    os.makedirs(obj_dir, exist_ok=True)
     sources = [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
     with concurrent.futures.ThreadPoolExecutor(max_workers=len(sources)) as ex:
-        results = list(ex.map(lambda s: _compile(s, verbose), sources))
+        results = list(ex.map(lambda s: _compile(s, verbose, obj_dir, defines), sources))
     if verbose:
         for _, log in results:
             sys.stderr.write(log)
-    cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH] + [o for o, _ in results]
+    cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib_path] + [o for o, _ in results]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
-    return LIB_PATH
+    return lib_path
+
+
+def _args_after(flag: str) -> list[str]:
+    return [sys.argv[i + 1] for i, a in enumerate(sys.argv[:-1]) if a == flag]
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    outs = _args_after("--out")
+    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                        defines=tuple(_args_after("--define")), out=outs[-1] if outs else None))
