@@ -518,6 +518,9 @@ def run_ours(args):
         dp = pkg.DataParallel(tnet, rank, world, parallel.handle_exchange(dist) if world > 1 else None)
         d_me = torch.zeros(1, dtype=torch.float32, device="cuda")
         dp.train_minibatch(d_timg, d_tlab, min(n_train, 8 * gb), gb, 1, 0.1, d_me, stream)      # warm-up
+        torch.cuda.synchronize()
+        if tnet.status() != 0:      # a bounded wait of the exchange ran out: report it instead of timing failed steps
+            raise RuntimeError("data-parallel exchange timed out during warm-up (rank %d of %d)" % (rank, world))
         barrier()
         res = {"global_batch": gb, "images": n_train, "epochs": CONFIG4_EPOCHS,
                "what": "benchmark configuration 4: fused fwd+bwd gradient kernel, then one kernel that reduces the rows, "

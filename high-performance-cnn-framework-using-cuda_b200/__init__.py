@@ -567,6 +567,21 @@ def persample_phase_clocks():
     return np.array(out[:], dtype=np.float64).reshape(4, 16)
 
 
+def forward_tc_phase_clocks():
+    """The same for the tensor-core forward kernel: float64 [16 warps][16 stamps] of CTA 0 of the last
+    launch (warp 0 finisher, 1 MMA issue, 2-3 loaders, 4-15 epilogue), or None without the
+    instrumented build."""
+    lib = load_library()
+    try:
+        fn = lib.cnn_debug_phase_clocks_tc
+    except AttributeError:
+        return None
+    out = (C.c_longlong * 256)()
+    fn.restype = C.c_int
+    _check(fn(out))
+    return np.array(out[:], dtype=np.float64).reshape(16, 16)
+
+
 def synth_images_device(seed: int, first_index: int, n: int, d_images, d_labels=None, stream=None) -> None:
     """Fill device buffers with synthetic images (and labels) -- same values as synth.synth_images."""
     _check(load_library().cnn_synth_images(int(seed), int(first_index), int(n), _ptr(d_images),

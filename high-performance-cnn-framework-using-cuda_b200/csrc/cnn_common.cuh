@@ -42,9 +42,12 @@ __device__ __forceinline__ float exp2f_approx(float x) {
 // step_function, layer.cu:81-84.  Three flavours, selected at compile time:
 //   0  the reference's own expression, compiled without fast-math (libdevice expf, IEEE divide):
 //      equal pre-activations give bit-equal activations; about 21 instructions;
-//   1  the short form, __expf and __fdividef (ex2.approx / rcp.approx, four dependent instructions):
-//      about 1e-6 relative from flavour 0 per evaluation for |v| <= 16 (the multiplication by log2e is
-//      rounded before the exponential).  What the fused kernels of the 28x28 net use when
+//   1  the short form: one multiply, ex2.approx.ftz, one add, rcp.approx.ftz -- four dependent
+//      instructions, written with the flush-to-zero forms explicitly (the non-ftz forms that
+//      __expf / __fdividef compile to without fast-math carry range checks and rescaling around
+//      each special-function instruction); a flushed subnormal only ever turns an activation of
+//      ~1e-38 into 0.  About 1e-6 relative from flavour 0 per evaluation for |v| <= 16 (the
+//      multiplication by log2e is rounded before the exponential).  What the fused kernels of the 28x28 net use when
 //      fast_sigmoid is set: on the network's outputs it is as close to the fp64 oracle as flavour 0
 //      (2.1e-6 over 65,536 images);
 //   2  the same two special-function instructions with the argument reduced in two FMA steps
@@ -53,7 +56,10 @@ __device__ __forceinline__ float exp2f_approx(float x) {
 template <int FLAVOR>
 __device__ __forceinline__ float sigmoidf(float v) {
   if constexpr (FLAVOR == 1) {
-    return __fdividef(1.0f, 1.0f + __expf(-v));
+    const float d = 1.0f + exp2f_approx(v * -1.4426950408889634f);
+    float q;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q) : "f"(d));
+    return q;
   } else if constexpr (FLAVOR == 2) {
     const float x = fminf(fmaxf(-v, -87.0f), 87.0f);
     const float magic = 12582912.0f;                       // 1.5 * 2^23: adding it rounds to integer

@@ -6,18 +6,18 @@
 // global batch (k_grad_partials), and ONE kernel per step then
 //   1. adds the rank's partial rows in fixed order (what k_reduce_rows does),
 //   2. stores the resulting 2,368-float vector into a per-source slot of EVERY rank's exchange
-//      buffer with ordinary stores through peer-mapped memory (NVLink), followed by a release flag
-//      per (source rank, block),
-//   3. waits -- bounded -- on its OWN buffer's flags until every rank's contribution has landed,
-//   4. adds the slots in rank order (so every rank computes bit-identical sums) and applies
+//      buffer through peer-mapped memory (NVLink).  Every element travels as ONE naturally aligned
+//      64-bit store carrying the value in its low half and the step number in its high half, so a
+//      word is its own arrival flag: no fence, no separate flag store, no second round trip,
+//   3. polls -- bounded -- its OWN buffer until every rank's word of this step has landed,
+//   4. adds the values in rank order (so every rank computes bit-identical sums) and applies
 //      params += scale * sum.
 // No TMA, no multicast, no load from a peer's memory: remote data always lands in the local buffer
 // first and is read from there.  A 9.5 KB all-reduce is pure latency; this replaces NCCL's launch,
-// protocol and second kernel by one store-and-flag round over NVLink inside a kernel that has to
-// run anyway.
+// protocol and second kernel by one one-way trip over NVLink inside a kernel that has to run anyway.
 //
-// Granularity: the kernel's blocks own 32 columns each and never talk to each other; block b only
-// waits for block b of the other ranks.  Step numbers live in device memory (one counter per block,
+// Granularity: the kernel's blocks own 32 columns each and never talk to each other; a lane only
+// waits for its own column of the other ranks.  Step numbers live in device memory (one counter per block,
 // advanced by the block itself), so a captured CUDA graph of steps can be replayed.  Slots alternate
 // with the step's parity: a rank can only be one step ahead of the slowest rank (it needs that
 // rank's data to finish a step), and its stores of step s+1 go to the other parity while a slow
@@ -35,8 +35,8 @@ constexpr int kDpRedGroups = 16;   // row groups per column: 512 threads per blo
 
 // Exchange buffer of one rank (device memory of that rank; every rank maps all of them).
 struct DpBuffer {
-  float slot[2][kDpMaxRanks][kRowStride];      // [step parity][source rank][column]
-  unsigned flag[kDpMaxRanks][kDpBlocks];       // [source rank][block]: last step whose data has landed
+  // [step parity][source rank][column]: value bits | step number << 32 (zero = nothing yet; steps count from 1)
+  unsigned long long slot[2][kDpMaxRanks][kRowStride];
   unsigned step[kDpBlocks];                    // local only: steps completed by block b of this rank
 };
 
@@ -44,17 +44,14 @@ struct DpPeers {
   DpBuffer* buf[kDpMaxRanks];
 };
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+// A naturally aligned 64-bit scalar access is single-copy atomic: a reader sees the whole word of
+// one store or none of it, never the step number of one store with the value of another.
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float ld_relaxed_sys(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
 
@@ -81,11 +78,9 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
 
   // (the pointer table is a kernel parameter: only compile-time indices keep it out of local memory)
   DpBuffer* mine = nullptr;
-  DpBuffer* of_lane = nullptr;   // lane r < world: rank r's buffer
 #pragma unroll
   for (int r = 0; r < kDpMaxRanks; ++r) {
     if (r == rank) mine = peers.buf[r];
-    if (r == lane) of_lane = peers.buf[r];
   }
   const unsigned seq = mine->step[b] + 1u;      // written only by this block, one launch ago
   const int parity = (int)(seq & 1u);
@@ -106,31 +101,32 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
     }
     return;
   }
-  if (send) {
-    if (col < kRowStride) {
+  if (send && col < kRowStride) {
+    const unsigned long long word = (unsigned long long)__float_as_uint(total) | ((unsigned long long)seq << 32);
 #pragma unroll
-      for (int r = 0; r < kDpMaxRanks; ++r)
-        if (r < world) peers.buf[r]->slot[parity][rank][col] = total;
-    }
-    __threadfence_system();     // this lane's stores are performed system-wide before what follows
-    __syncwarp();
-    if (lane < world) st_release_sys(&of_lane->flag[rank][b], seq);
+    for (int r = 0; r < kDpMaxRanks; ++r)
+      if (r < world) st_relaxed_sys_u64(&peers.buf[r]->slot[parity][rank][col], word);
   }
-  // ---- wait for every rank's block b (own buffer only), bounded ---------------------------------
+  // ---- collect every rank's word of this step for this lane's column (own buffer only), bounded ----
   bool ok = true;
-  if (lane < world) {
-    const unsigned* f = &mine->flag[lane][b];
-    if ((int)(ld_acquire_sys(f) - seq) < 0) {
-      const long long t0 = clock64();
-      unsigned spins = 0;
-      while ((int)(ld_acquire_sys(f) - seq) < 0) {
+  float sum = 0.f;
+  if (col < kRowStride) {
+    long long t0 = 0;
+    unsigned spins = 0;
+    for (int r = 0; r < world && ok; ++r) {
+      const unsigned long long* w = &mine->slot[parity][r][col];
+      unsigned long long v = ld_relaxed_sys_u64(w);
+      while ((unsigned)(v >> 32) != seq) {
+        if (t0 == 0) t0 = clock64();
         // a wait that ran out anywhere on this GPU ends the others soon after
         const bool other = ((++spins & 255u) == 0) && *reinterpret_cast<volatile int*>(status) != 0;
         if (other || clock64() - t0 > wait_clocks) {
           ok = false;
           break;
         }
+        v = ld_relaxed_sys_u64(w);
       }
+      sum += __uint_as_float((unsigned)v);     // rank order: every rank adds the same values in the same order
     }
   }
   ok = __all_sync(0xffffffffu, ok);
@@ -142,8 +138,6 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
     return;   // parameters are left as they are: the step is reported as failed, not half applied
   }
   if (col < kRowStride) {
-    float sum = 0.f;
-    for (int r = 0; r < world; ++r) sum += ld_relaxed_sys(&mine->slot[parity][r][col]);
     if (G) G[col] = sum;
     if (col < kNParams) params[col] = fmaf(scale, sum, params[col]);
     if (mean_err && col == kRowErr) *mean_err += err_scale * sum;

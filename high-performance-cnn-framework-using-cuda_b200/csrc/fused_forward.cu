@@ -3,7 +3,7 @@
 // the reference's forward_pass launch sequence (main.cu:67-88: 8 memsets, one H2D copy and nine
 // <<<64,64>>> launches per image) and classify's D2H + host argmax (main.cu:181-189).
 //
-// Data movement: images are contiguous 3,136-byte records, so a tile of 8 images is one 25 KB
+// Data movement: images are contiguous 3,136-byte records, so a tile of 7 images is one 22 KB
 // 1-D bulk copy (cp.async.bulk, no multicast) into shared memory, double-buffered behind
 // mbarriers; the only other HBM traffic is the 44 bytes of results per image.
 //
@@ -15,13 +15,16 @@
 
 namespace cnn {
 
-constexpr int kFwImgs = 8;                  // images per tile
-constexpr int kFwThreads = kFwImgs * 36;    // 288 = 9 warps
+// Seven images per tile: 252 of a block's 256 threads own a window, and two 8-warp blocks per SM may use
+// 128 registers per thread.  (Eight images = 288 threads are allocated as ten warps, which caps two
+// blocks per SM at 96 registers: 0.387 ms per 65,536 images against 0.333 ms with this shape.)
+constexpr int kFwImgs = 7;                                    // images per tile
+constexpr int kFwThreads = (kFwImgs * 36 + 31) / 32 * 32;    // 256 = 8 warps
 constexpr int kFwStages = 2;
 constexpr int kPartStride = 37;             // 36 windows + 1 pad: conflict-free column reads
 
 struct FwSmem {
-  float img[kFwStages][kFwImgs][kImg];      // 2 x 25,088 B, filled by bulk copies
+  float img[kFwStages][kFwImgs][kImg];      // 2 x 21,952 B, filled by bulk copies
   float wc[kF][28];                         // 25 taps padded to 28 for 128-bit loads
   float bc[8];
   float ws[16];
@@ -174,7 +177,7 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
     __syncthreads();
 
     // Three images per warp on lanes 0..29: lane = 10*local_image + k.
-    if (warp < 3) {
+    if (warp < (kFwImgs + 2) / 3) {
       const int li = lane / 10, k = lane % 10;
       const int im = warp * 3 + li;
       const bool valid = (lane < 30) && (im < imgs_here);
@@ -205,7 +208,7 @@ k_fused_forward(const float* __restrict__ images, long n, const float* __restric
 template <int FAST, bool U8, int UNROLL>
 static int launch_variant(cnn_net* net, const void* d_images, long n, float* d_out, int* d_argmax,
                           cudaStream_t stream) {
-  constexpr int kMinBlocks = 2;   // two 9-warp blocks per SM: 96 registers per thread
+  constexpr int kMinBlocks = 2;   // two 8-warp blocks per SM: 128 registers per thread
   const long n_tiles = (n + kFwImgs - 1) / kFwImgs;
   const long max_blocks = (long)kMinBlocks * sm_count();
   const int grid = (int)(n_tiles < max_blocks ? n_tiles : max_blocks);
@@ -219,9 +222,8 @@ static int launch_variant(cnn_net* net, const void* d_images, long n, float* d_o
   return CNN_OK;
 }
 
-// fast_sigmoid set (the default): the short sigmoid form, 0.387 ms per 65,536 images against 0.447 ms
-// for the refined form (map loop unrolled by two) and 0.546 ms for the reference expression; over that
-// batch all three are equally close to the fp64 oracle (2.1e-6; the fp32 oracle itself is 4.0e-6 away).
+// fast_sigmoid set (the default): the short sigmoid form, 0.333 ms per 65,536 images; over that batch it
+// is as close to the fp64 oracle as the reference expression (2.1e-6; the fp32 oracle itself is 4.0e-6 away).
 int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
                    cudaStream_t stream) {
   if (net->forward_path != 0) return forward_device_tc(net, d_images, n, d_out, d_argmax, stream);

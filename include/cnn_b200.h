@@ -250,8 +250,9 @@ int cnn_grad_batch_noalloc_status(void* stream);
  * there is no collective in layer.cu / main.cu); the per-step arithmetic is cnn_train_minibatch's.
  * Every rank computes the summed gradient of its slice of a global batch; one kernel per step then
  * reduces the rank's partial rows, stores the 2368-float vector into a per-source slot of every
- * rank's exchange buffer (ordinary stores through peer-mapped memory over NVLink, then a release
- * flag), waits -- bounded -- on its own buffer for all ranks' contributions, adds them in rank order
+ * rank's exchange buffer (through peer-mapped memory over NVLink; every element travels as one
+ * 64-bit word holding the value and the step number, so a word is its own arrival flag), polls --
+ * bounded -- its own buffer for all ranks' words of the step, adds the values in rank order
  * and applies params += (dt / global_batch) * sum.  All ranks add the same values in the same order,
  * so their parameters stay bit-identical.  A wait that runs out (a rank that never sent) leaves the
  * parameters of that step untouched and is reported by cnn_net_status as CNN_ERR_TIMEOUT.
