@@ -7,7 +7,8 @@
 #include "net.cuh"
 
 namespace cnn {
-int forward_device(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+int forward_kernel_for(const cnn_net* net, long n_total);
+int forward_device(cnn_net* net, int path, const float* d_images, long n, float* d_out, int* d_argmax,
                    cudaStream_t stream);
 int forward_device_u8(cnn_net* net, const unsigned char* d_pixels, long n, float* d_out, int* d_argmax,
                       cudaStream_t stream);
@@ -140,7 +141,7 @@ int cnn_net_set_option(cnn_net* net, const char* key, int value) {
     return CNN_OK;
   }
   if (std::strcmp(key, "forward_path") == 0) {
-    CNN_REQUIRE(value >= 0 && value <= 2, "cnn_net_set_option: forward_path takes 0, 1 or 2");
+    CNN_REQUIRE(value >= -1 && value <= 2, "cnn_net_set_option: forward_path takes -1 (by batch size), 0, 1 or 2");
     net->forward_path = value;
     return CNN_OK;
   }
@@ -188,6 +189,7 @@ static int forward_host_impl(cnn_net* net, const void* h_images, bool u8, long n
   // D2H of chunk c).
   long done = 0;
   int slot = 0;
+  const int path = forward_kernel_for(net, n);     // one kernel for the whole request, whatever the chunking
   while (done < n) {
     const long cnt = (n - done) < net->stage_images ? (n - done) : net->stage_images;
     cudaStream_t st = net->copy_stream[slot];
@@ -196,7 +198,7 @@ static int forward_host_impl(cnn_net* net, const void* h_images, bool u8, long n
                              (size_t)cnt * image_bytes, cudaMemcpyHostToDevice, st));
     rc = u8 ? forward_device_u8(net, reinterpret_cast<const unsigned char*>(net->d_stage_img[slot]), cnt,
                                 net->d_stage_out[slot], net->d_stage_arg[slot], st)
-            : forward_device(net, net->d_stage_img[slot], cnt, net->d_stage_out[slot],
+            : forward_device(net, path, net->d_stage_img[slot], cnt, net->d_stage_out[slot],
                              net->d_stage_arg[slot], st);
     if (rc != CNN_OK) return rc;
     if (h_out)

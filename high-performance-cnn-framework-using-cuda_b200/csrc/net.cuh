@@ -7,8 +7,9 @@ struct cnn_net {
   int device = 0;
   unsigned seed = 0;               // what cnn_net_create drew the initial parameters from (kept for checkpoints)
   int ps_kernel = 1;               // per-sample SGD: 1 = six-CTA cluster kernel (default), 0 = single persistent block
-  int forward_path = 0;            // batched forward: 0 = exact fp32 SIMT kernel (default), 1 = tensor cores in three
-                                   // tf32 passes (fp32-level accuracy), 2 = tensor cores, one tf32 pass + tanh sigmoid
+  int forward_path = -1;           // batched forward: 0 = exact fp32 SIMT kernel, 1 = tensor cores in three tf32 passes
+                                   // (fp32-level accuracy), 2 = tensor cores, one tf32 pass + tanh sigmoid,
+                                   // -1 (default) = 1 for batches of kTcMinBatch images or more, else 0
   float* d_params = nullptr;       // kNParamsPadded floats
   int* d_status = nullptr;         // device status word: 0 ok, non-zero = a bounded wait ran out
   int fast_sigmoid = 1;            // sigmoid of the fused kernels: 0 = reference expression, 1 = short form (default)
@@ -91,7 +92,7 @@ constexpr int kRowStride = kNParamsPadded + 8;
 constexpr int kRowErr = kNParams + 1;  // 2344
 
 // Batched forward with the convolution on the tensor cores (forward_tc.cu): net->forward_path 1 or 2.
-int forward_device_tc(cnn_net* net, const float* d_images, long n, float* d_out, int* d_argmax,
+int forward_device_tc(cnn_net* net, int path, const float* d_images, long n, float* d_out, int* d_argmax,
                       cudaStream_t stream);
 int ensure_train_scratch(cnn_net* net, int rows);
 // Blocks of the minibatch gradient kernel for a batch of n images (one partial row per block).

@@ -176,11 +176,14 @@ int cnn_synth_images(unsigned long long seed, long first_index, long n, float* d
                      unsigned int* d_labels, void* stream);
 
 /* Options, by name:
- *   "forward_path"     kernel behind cnn_forward_batched (fp32 images): 0 (default) = exact fp32 on the
- *                      CUDA cores; 1 = the convolution on the tensor cores (tcgen05) in three tf32
- *                      passes, fp32-level accuracy, same 1e-5 parity bar; 2 = one tf32 pass and a
- *                      tanh.approx sigmoid: about 1e-3 on the outputs, argmax equal wherever the
- *                      top-two margin is clear of that -- an explicitly reduced-precision inference mode;
+ *   "forward_path"     kernel behind cnn_forward_batched (fp32 images): 0 = exact fp32 on the CUDA
+ *                      cores; 1 = the convolution on the tensor cores (tcgen05) in three tf32 passes,
+ *                      fp32-level accuracy, same 1e-5 parity bar; -1 (default) = 1 for batches of 6,144
+ *                      images or more (where it is the faster one) and 0 below, or always 0 when the
+ *                      reference's sigmoid expression is selected; 2 = one tf32 pass and a tanh.approx
+ *                      sigmoid: about 1e-4 on the outputs, argmax equal wherever the top-two margin is
+ *                      clear of that -- an explicitly reduced-precision inference mode, never chosen
+ *                      unless asked for;
  *   "persample_kernel" kernel of cnn_train_sgd_persample: 1 (default) = a cluster of six CTAs, one per
  *                      feature map, exchanging partial sums by one-way stores counted on mbarriers;
  *                      0 = one persistent block (no cluster launch needed), about half the speed;

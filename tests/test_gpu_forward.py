@@ -54,23 +54,26 @@ def test_forward_matches_oracle(cuda, pkg, ob, params0, n, fast):
     assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
 
 
+@pytest.mark.parametrize("path", [-1, 0])
 @pytest.mark.parametrize("fast", [0, 1])
-def test_full_size_forward_matches_oracle(cuda, pkg, ob, params0, fast):
+def test_full_size_forward_matches_oracle(cuda, pkg, ob, params0, fast, path):
     """Benchmark configuration 2 at its full size: 65,536 images of seed 1 against the oracle --
     every sigmoid within 1e-5 relative, argmax equal on every clear-margin row; the number of rows
     below the margin and the number of differing rows are printed (both are expected to be zero or a
-    handful out of 65,536)."""
+    handful out of 65,536).  Run with the default kernel choice (at this size and with the short sigmoid
+    form: the three-pass tensor-core kernel) and with the CUDA-core kernel forced."""
     n = 65536
     images, _ = pkg.synth.synth_images(1, n)
     net = pkg.Net(0)
     net.set_params(params0)
     net.set_fast_sigmoid(fast)
+    net.set_option("forward_path", path)
     out, arg = run_forward(cuda, net, images)
     ref_out, ref_arg = ob.forward_batch(params0, images, threads=0)
     err = rel_err(out, ref_out)
-    print("full size, flavour %d: max relative error of the sigmoids %.3e" % (fast, err))
+    print("full size, flavour %d, forward_path %d: max relative error of the sigmoids %.3e" % (fast, path, err))
     assert err < 1e-5
-    check_argmax(arg, ref_arg, ref_out, "65,536 images flavour %d" % fast)
+    check_argmax(arg, ref_arg, ref_out, "65,536 images flavour %d path %d" % (fast, path))
     assert np.array_equal(arg, np.argmax(out, axis=1).astype(np.int32))
 
 
@@ -153,13 +156,16 @@ def test_forward_against_reference_kernels(cuda, pkg, ob, params0):
     check_argmax(arg, ref_arg, ref_out, "96 images against the reference kernels", max_masked_frac=0.05)
 
 
-def test_full_size_property_linearity_in_batch(cuda, pkg, params0):
+@pytest.mark.parametrize("path", [-1, 0])
+def test_full_size_property_linearity_in_batch(cuda, pkg, params0, path):
     """benchmark configuration 2 size (65,536 images): results of a batch do not depend on where an image
     sits in it -- the full batch equals the concatenation of two half batches, bit for bit, and the
-    device generator fills the same images as the host generator."""
+    device generator fills the same images as the host generator.  Holds for the default kernel choice
+    (tensor cores at these sizes) and for the CUDA-core kernel."""
     n = 65536
     net = pkg.Net(0)
     net.set_params(params0)
+    net.set_option("forward_path", path)
     d_img = cuda.empty((n, 28, 28), dtype=cuda.float32, device="cuda")
     pkg.synth_images_device(1, 0, n, d_img)
     d_out = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
@@ -189,11 +195,13 @@ def test_device_generator_matches_host(cuda, pkg):
 
 @pytest.mark.parametrize("n", [1, 9, 1000, 8192 + 77])
 def test_uint8_input_is_bit_identical_to_fp32(cuda, pkg, params0, n):
-    """uint8 pixels through the in-kernel pixel/255.0 table == fp32 images through the fp32 kernel."""
+    """uint8 pixels through the in-kernel pixel/255.0 table == fp32 images through the fp32 kernel
+    (the CUDA-core kernel, which is the one that has the uint8 ingest)."""
     pix = pkg.synth.synth_pixels_u8(26, n)
     images = pkg.synth.u8_to_float(pix)
     net = pkg.Net(0)
     net.set_params(params0)
+    net.set_option("forward_path", 0)
     out_f, arg_f = run_forward(cuda, net, images)
     d_pix = cuda.from_numpy(pix).cuda()
     d_out = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
@@ -222,6 +230,7 @@ def test_sigmoid_flavours_agree(cuda, pkg, ob, params0):
         net = pkg.Net(0)
         net.set_params(params0)
         net.set_fast_sigmoid(fl)
+        net.set_option("forward_path", 0)      # the same kernel for both forms
         o = cuda.empty((n, 10), dtype=cuda.float32, device="cuda")
         net.forward(d_img, n, o, None)
         cuda.cuda.synchronize()
@@ -318,3 +327,27 @@ def test_tensor_core_forward_optional_outputs_and_host_pipeline(cuda, pkg, param
     h_arg = np.empty((n,), dtype=np.int32)
     net.forward_host(images, n, h_out, h_arg)
     assert np.array_equal(h_out, out) and np.array_equal(h_arg, arg)
+
+
+def test_default_kernel_choice_follows_batch_size(cuda, pkg, params0):
+    """forward_path = -1 (the default): below 6,144 images per call the CUDA-core kernel answers, from
+    6,144 on the three-pass tensor-core kernel -- bit for bit in both cases; with the reference's
+    sigmoid expression selected the default stays on the CUDA-core kernel at every size."""
+    images, _ = pkg.synth.synth_images(29, 6144)
+    outs = {}
+    for path in (-1, 0, 1):
+        net = pkg.Net(0)
+        net.set_params(params0)
+        net.set_option("forward_path", path)
+        outs[path] = (run_forward(cuda, net, images[:6143]), run_forward(cuda, net, images))
+    assert np.array_equal(outs[-1][0][0], outs[0][0][0]) and np.array_equal(outs[-1][0][1], outs[0][0][1])
+    assert np.array_equal(outs[-1][1][0], outs[1][1][0]) and np.array_equal(outs[-1][1][1], outs[1][1][1])
+    assert not np.array_equal(outs[0][1][0], outs[1][1][0])     # the two kernels do differ in the last bits
+    ref = {}
+    for path in (-1, 0):
+        net = pkg.Net(0)
+        net.set_params(params0)
+        net.set_fast_sigmoid(0)
+        net.set_option("forward_path", path)
+        ref[path] = run_forward(cuda, net, images)
+    assert np.array_equal(ref[-1][0], ref[0][0])
