@@ -59,7 +59,7 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
 // send == 0 is host-side fault injection for the tests: the rank keeps its vector to itself (its own
 // slot included), so that every rank's bounded wait runs out.
 __global__ void __launch_bounds__(32 * kDpRedGroups)
-k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers peers, int rank, int world,
+k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers peers, DpBuffer* mine, int rank, int world,
                          float* __restrict__ params, float scale, float* __restrict__ G,
                          float* __restrict__ mean_err, float err_scale, long long wait_clocks, int send,
                          int* __restrict__ status) {
@@ -67,6 +67,11 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
   const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
   const int b = blockIdx.x;
   const int col = b * 32 + lane;
+  // (`mine` is this rank's own buffer, peers.buf[rank], passed separately: the pointer table is a kernel
+  // parameter and only compile-time indices keep it out of local memory -- with a 64-byte stack frame
+  // for it this kernel took 12 us instead of 6)
+  unsigned seq = 0;
+  if (world > 1 && g == 0) seq = mine->step[b] + 1u;   // written only by this block, one launch ago; in flight under the row sums
   float acc = 0.f;
   if (col < kRowStride) {
 #pragma unroll 4
@@ -76,14 +81,6 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
   __syncthreads();
   if (g != 0) return;
 
-  // (the pointer table is a kernel parameter: only compile-time indices keep it out of local memory)
-  DpBuffer* mine = nullptr;
-#pragma unroll
-  for (int r = 0; r < kDpMaxRanks; ++r) {
-    if (r == rank) mine = peers.buf[r];
-  }
-  const unsigned seq = mine->step[b] + 1u;      // written only by this block, one launch ago
-  const int parity = (int)(seq & 1u);
   float total;
   {
     float q[4];
@@ -101,6 +98,7 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
     }
     return;
   }
+  const int parity = (int)(seq & 1u);
   if (send && col < kRowStride) {
     const unsigned long long word = (unsigned long long)__float_as_uint(total) | ((unsigned long long)seq << 32);
 #pragma unroll
@@ -277,7 +275,7 @@ int cnn_dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels,
   const int send = dp->drop_next_send ? 0 : 1;
   dp->drop_next_send = 0;
   k_reduce_exchange_update<<<kDpBlocks, 32 * kDpRedGroups, 0, st>>>(
-      net->d_partials, grid, dp->peers, dp->rank, dp->world, net->d_params, scale, d_grad_sum, d_mean_err,
+      net->d_partials, grid, dp->peers, dp->local, dp->rank, dp->world, net->d_params, scale, d_grad_sum, d_mean_err,
       err_scale, wait_clocks, send, net->d_status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_reduce_exchange_update launch");
