@@ -58,7 +58,7 @@ SIGMOID_NAMES = {0: "reference expression (expf + IEEE divide)",
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch over 65,536 images, per forward path,
 # from the ncu captures summarised under profiles/ (k_fused_forward_*, k_forward_tc_*).
-TRAFFIC_BYTES_PER_LAUNCH = {0: 210699776, 1: 211484160, 2: 211919360}
+TRAFFIC_BYTES_PER_LAUNCH = {0: 210611456, 1: 211582976, 2: 211068160}
 
 
 def measured_peak_gbs():
