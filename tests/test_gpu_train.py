@@ -137,6 +137,55 @@ def test_persample_trajectory_matches_oracle(cuda, pkg, ob, params0, fast):
     assert (d_arg.cpu().numpy() == arg_or).mean() > 0.99
 
 
+def test_full_size_persample_epoch_matches_oracle(cuda, pkg, ob, params0):
+    """Benchmark configuration 1 at its full size: one epoch of per-sample SGD over 10,000 images of
+    seed 0 in file order, then the argmax of 2,000 held-out images, against the oracle run on the
+    same data.  10,000 sequential steps compound rounding differences, so the parameters are held to
+    2e-3 of the largest parameter (printed), the epoch's mean error to 1e-4 relative and the test-set
+    predictions to 99 % agreement (labels are random, so accuracy itself is chance for both)."""
+    n_train, n_test = 10000, 2000
+    images, labels = pkg.synth.synth_images(0, n_train + n_test)
+    d_img, d_lab = to_dev(cuda, images, labels)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    ran, mean_err = net.train_sgd_persample(d_img, d_lab, n_train, 1)
+    p_or, m_or, ran_or = ob.train_persample(params0, images[:n_train], labels[:n_train], 1)
+    err = scaled_err(net.get_params(), p_or)
+    print("10,000 steps: parameter distance %.3e, mean error %.6f vs oracle %.6f" % (err, float(mean_err[0]), float(m_or[0])))
+    assert ran == ran_or == 1
+    assert err < 2e-3
+    assert np.allclose(mean_err, m_or, rtol=1e-4)
+    d_arg = cuda.empty((n_test,), dtype=cuda.int32, device="cuda")
+    net.forward(d_img[n_train:], n_test, None, d_arg)
+    cuda.cuda.synchronize()
+    _, arg_or = ob.forward_batch(p_or, images[n_train:])
+    agree = float((d_arg.cpu().numpy() == arg_or).mean())
+    acc = float((d_arg.cpu().numpy().astype(np.uint32) == labels[n_train:]).mean())
+    acc_or = float((arg_or.astype(np.uint32) == labels[n_train:]).mean())
+    print("test set: %.4f of the predictions agree; accuracy %.4f vs oracle %.4f" % (agree, acc, acc_or))
+    assert agree > 0.99 and abs(acc - acc_or) < 0.01
+
+
+def test_full_size_minibatch_epoch_matches_oracle(cuda, pkg, ob, params0):
+    """Benchmark configuration 4 at its full single-GPU size: one epoch of minibatch SGD, batch 256,
+    over 60,000 images of seed 3, against the oracle's minibatch rule: parameters within 2e-5 of the
+    largest parameter, the epoch's mean error within 1e-5 relative."""
+    n, batch = 60000, 256
+    images, labels = pkg.synth.synth_images(3, n)
+    d_img, d_lab = to_dev(cuda, images, labels)
+    net = pkg.Net(0)
+    net.set_params(params0)
+    d_me = cuda.zeros(1, dtype=cuda.float32, device="cuda")
+    net.train_minibatch(d_img, d_lab, n, batch, 1, 0.1, d_me)
+    cuda.cuda.synchronize()
+    assert net.status() == 0
+    p_or, me_or = ob.train_minibatch(params0, images, labels, batch, 1)
+    err = scaled_err(net.get_params(), p_or)
+    print("235 steps of 256: parameter distance %.3e, mean error %.7f vs oracle %.7f" % (err, float(d_me.item()), float(me_or[0])))
+    assert err < 2e-5
+    assert np.allclose(d_me.cpu().numpy(), me_or, rtol=1e-5)
+
+
 def test_persample_early_stop_and_determinism(cuda, pkg, params0):
     images, labels = pkg.synth.synth_images(36, 200)
     d_img, d_lab = to_dev(cuda, images, labels)
