@@ -22,7 +22,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libcnn_b200.so")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 
 SOURCES = ["layer_abi.cu", "net.cu", "checkpoint.cu", "fused_forward.cu", "forward_tc.cu", "fused_train.cu", "dp_exchange.cu",
-           "persample_cluster8.cu", "wide.cu", "wide_tc.cu", "synth.cu"]
+           "persample_cluster8.cu", "wide.cu", "wide_tc.cu", "wide_grad_tc.cu", "synth.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

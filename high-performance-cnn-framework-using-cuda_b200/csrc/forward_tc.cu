@@ -96,15 +96,6 @@ __device__ __forceinline__ long long global_ns() {
 #define TC_CTA_TIME(i) do { } while (0)
 #endif
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 // Eight consecutive fp32 columns of this warp's 32 tensor-memory lanes; not waited for.
 __device__ __forceinline__ void tmem_ld8_nowait(unsigned taddr, unsigned (&r)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"

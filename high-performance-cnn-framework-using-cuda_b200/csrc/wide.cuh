@@ -33,6 +33,11 @@ struct cnn_wide {
   int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)
   int* d_status = nullptr;      // bounded-wait status word
   long part_rows = 0;           // rows of [F][26] that part_c holds
+  // Tensor map (a CUtensorMap, kept opaque here) through which the weight-gradient kernel reads dc, and what it
+  // was encoded for.
+  alignas(64) unsigned char dc_map[128] = {};
+  const float* dc_map_ptr = nullptr;
+  long dc_map_cap = 0;
 };
 
 

@@ -1,0 +1,419 @@
+// Conv weight gradient of the widened configuration on the tensor cores (tcgen05), as a pipeline
+// fed by TMA.
+//
+//   G[f][t] = sum_m dc[m][f] * A[m][t]      m = (image, output position), t = filter tap
+//
+// with A the im2col rows of the forward convolution and dc the conv deltas (already divided by C*C).
+// As an MMA:  D[M = F = 64][N = 32] += dcT[64][K = TP positions] * im2colT[32][K = TP positions], both
+// operands K-major (dcT with the 128-byte swizzle, im2colT in the canonical un-swizzled layout); tap
+// 25, unused by the filter, is a row of ones so that column 25 of D is the conv-bias gradient (taps
+// 26..31 are rows of zeros).  A tile is
+// TP consecutive positions of ONE image (the last tile of an image is ragged: the positions past
+// the image read as zeros).
+//
+// One CTA per SM, thirteen warps, four stages of 48 KB in shared memory:
+//   * the dcT tile (64 maps x TP positions, 32 KB at TP = 128) comes in by TMA: dc is stored per
+//     (image, map) with positions contiguous, a 3-D tensor map (position, map, image) with a box of
+//     32 positions x 64 maps and the 128-byte swizzle writes one K-block of the operand (64 rows of
+//     128 bytes) per cp.async.bulk.tensor, and the MMA reads it through a SWIZZLE_128B descriptor.
+//     (Copying the tile with per-thread cp.async stalled at 2 TB/s -- the copies of one tile took
+//     4,000 cycles to get into the load/store pipeline -- and a tensor map that produced the
+//     un-swizzled core-matrix layout directly, with 16-byte inner boxes, ran at 2.7 TB/s: the TMA
+//     wants long inner rows.)  No multicast; positions past the image are filled with zeros;
+//   * warps 1-3 and 12 copy the im2colT tile with 4-byte cp.async: a warp instruction covers 8 taps x
+//     4 consecutive positions = one 128-byte core matrix of the operand (conflict-free), read as 8
+//     segments of 16 contiguous bytes of the image (L1/L2-resident);
+//   * in the three-pass mode (hi*hi + lo*hi + hi*lo, fp32-level accuracy) warps 8-11 split the dcT
+//     tile in place into a tf32-exact high tile and a remainder tile once it has landed, and the
+//     im2col warps split what they copied; in the one-pass mode the tensor core reads the fp32
+//     values as they are;
+//   * warp 0 issues the MMAs (an elected lane of the converged warp) and commits to mbarriers;
+//   * warps 4-7 (one per 32-lane quarter of tensor memory) move the accumulator into registers every
+//     256 positions and add it there: the tensor core adds into its fp32 accumulator with truncation,
+//     about one ulp of the running sum per MMA, which over the ~150 tiles of a CTA at batch 1,024
+//     would leave the gradient 5e-5 from the fp64 oracle.  Two accumulators alternate, so the MMA
+//     warp never waits for a flush.
+// Every wait is bounded; a wait that runs out sets the status word and lets the kernel finish.
+// At the end every CTA writes one partial [F][26]; k_wide_reduce adds the partials in CTA order.
+#include <cuda.h>
+
+#include "wide.cuh"
+#include "wide_tc.cuh"
+#include "phase_clocks.cuh"
+
+namespace cnn {
+
+constexpr int kGtStages = 4;
+constexpr int kGtStageBytes = 48 * 1024;
+constexpr int kGtThreads = 13 * 32;
+constexpr int kGtF = 64;
+
+struct GtBarriers {
+  unsigned long long landed[kGtStages], full[kGtStages], free[kGtStages], acc_full[2], acc_free[2];
+  unsigned tmem_base;
+  long long clock_base;    // phase clocks only
+};
+
+CNN_PHASE_TABLE(g_phase_clocks_wg, 13)
+
+// One 3-D box of the tensor behind `map` into shared memory; completes its bytes on the mbarrier.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory descriptor of a K-major operand stored with the 128-byte swizzle: rows of 128 bytes (32 tf32
+// values of K), eight rows per 1,024-byte atom (SBO), the 16-byte chunks of a row XOR-ed with the row number
+// -- what a TMA box with CU_TENSOR_MAP_SWIZZLE_128B writes.  Layout type 2 in bits 61-63, version 1.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= 1ull << 16;                        // leading byte offset: not used by swizzled K-major operands
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+constexpr unsigned kGtKBlock = 64 * 128;   // bytes of one K-block of the dcT operand: 64 maps x 32 positions
+
+// TP = positions per tile (K of one tile): 128 with one pass, 64 with three (the stage then holds a high and
+// a low tile of each operand).
+template <int TP, int PASSES>
+__global__ void __launch_bounds__(kGtThreads, 1)
+k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap dc_map, const float* __restrict__ images, long n,
+                    float* __restrict__ part, int* __restrict__ status) {
+  constexpr int CH = TP / 4;                          // 16-byte chunks along K
+  constexpr unsigned kGroup = tc::tile_group_stride(CH);
+  constexpr unsigned kABytes = (kGtF / 8) * kGroup;   // TP * 256
+  constexpr unsigned kBBytes = 4 * kGroup;            // 32 tap rows: TP * 128
+  constexpr unsigned kLoOff = kABytes + kBBytes;      // low tiles behind the high ones
+  static_assert((PASSES == 3 ? 2 : 1) * (kABytes + kBBytes) == (unsigned)kGtStageBytes, "stage size");
+  constexpr int kAhead = kGtStages - 1;               // tiles in flight beyond the one being handed over
+  constexpr int kFlushTiles = 256 / TP;               // tiles per accumulator hand-over
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* stage0 = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  GtBarriers& bars = *reinterpret_cast<GtBarriers*>(stage0 + kGtStages * kGtStageBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int CC = d.C * d.C;
+  const int tiles_per_image = (CC + TP - 1) / TP;
+  const long n_tiles = n * tiles_per_image;
+  const int my_tiles = (blockIdx.x < n_tiles) ? (int)((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+
+  // ---- set-up: all stages zero (stale operand bytes must at least be finite), the row of ones, barriers ----
+  for (int i = tid; i < kGtStages * kGtStageBytes / 16; i += kGtThreads)
+    reinterpret_cast<float4*>(stage0)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncthreads();
+  for (int i = tid; i < kGtStages * TP; i += kGtThreads) {
+    const int s = i / TP, p = i % TP;
+    *reinterpret_cast<float*>(stage0 + s * kGtStageBytes + kABytes + tc::tile_offset(25, p >> 2, CH) + (p & 3) * 4) = 1.0f;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kGtStages; ++s) {
+      mbar_init(&bars.landed[s], 1);      // the producer's arrive.expect_tx; the TMA completes the bytes
+      mbar_init(&bars.full[s], 8);        // one arrival per loader warp
+      mbar_init(&bars.free[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars.acc_full[a], 1);
+      mbar_init(&bars.acc_free[a], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 0) tc::tmem_alloc(&bars.tmem_base, 64);
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const unsigned tmem_d = bars.tmem_base;
+
+  bool gave_up = false;
+  CNN_PHASE_BEGIN(blockIdx.x == 0, bars.clock_base)
+  const int n_groups = (my_tiles + kFlushTiles - 1) / kFlushTiles;
+
+  // tile kk of this CTA: image and first position in it
+  auto tile_origin = [&](int kk, long& b, int& pos0) {
+    const long t = (long)blockIdx.x + (long)kk * gridDim.x;
+    b = t / tiles_per_image;
+    pos0 = (int)(t - b * tiles_per_image) * TP;
+  };
+
+  if (warp == 0) {
+    // ================= MMA issue ====================================================================
+    const unsigned idesc = tc::idesc_tf32(kGtF, 32, 0, 0);
+    for (int k = 0; k < my_tiles; ++k) {
+      const int s = k % kGtStages;
+      const int grp = k / kFlushTiles, acc = grp & 1;
+      const bool first = (k % kFlushTiles) == 0;
+      CNN_PHASE(0);
+      if (first) mbar_wait_bounded(&bars.acc_free[acc], ((unsigned)(grp >> 1) & 1u) ^ 1u, status, gave_up);
+      CNN_PHASE(1);
+      mbar_wait_bounded(&bars.full[s], (unsigned)(k / kGtStages) & 1u, status, gave_up);
+      CNN_PHASE(2);
+      __syncwarp();
+      tc::fence_after_sync();
+      const unsigned base = smem_u32(stage0 + s * kGtStageBytes);
+      unsigned accumulate = first ? 0u : 1u;
+#pragma unroll 1
+      for (int pass = 0; pass < PASSES; ++pass) {
+        const unsigned a_s = base + ((pass == 1) ? kLoOff : 0u);
+        const unsigned b_s = base + kABytes + ((pass == 2) ? kLoOff : 0u);
+#pragma unroll
+        for (int ks = 0; ks < TP / 8; ++ks) {          // 8 positions per MMA = two 16-byte chunks
+          const unsigned long long ad = smem_desc_sw128(a_s + (unsigned)(ks >> 2) * kGtKBlock + (unsigned)(ks & 3) * 32u);
+          const unsigned long long bd = tc::smem_desc(b_s + ks * 256, 128, kGroup);
+          tc::mma_tf32_elect(tmem_d + (unsigned)(acc * 32), ad, bd, idesc, accumulate);
+          accumulate = 1;
+        }
+      }
+      tc::mma_commit_elect(&bars.free[s]);
+      if ((k % kFlushTiles) == kFlushTiles - 1 || k == my_tiles - 1) tc::mma_commit_elect(&bars.acc_full[acc]);
+      CNN_PHASE(3);
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ================= accumulator flush and the CTA's partial ======================================
+    float racc[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) racc[c] = 0.f;
+    const unsigned lane_base = tmem_d + ((unsigned)((warp & 3) * 32) << 16);
+    for (int g = 0; g < n_groups; ++g) {
+      const int acc = g & 1;
+      CNN_PHASE(0);
+      mbar_wait_bounded(&bars.acc_full[acc], (unsigned)(g >> 1) & 1u, status, gave_up);
+      CNN_PHASE(1);
+      tc::fence_after_sync();
+#pragma unroll
+      for (int c0 = 0; c0 < 32; c0 += 16) {
+        float v[16];
+        tc::tmem_ld16(lane_base + (unsigned)(acc * 32 + c0), v);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) racc[c0 + e] += v[e];
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.acc_free[acc]);
+      CNN_PHASE(2);
+    }
+    // M = 64: lanes 0..15 of quarter w hold maps 16 w + lane
+    if (lane < 16) {
+      float* dst = part + ((size_t)blockIdx.x * kGtF + 16 * (warp & 3) + lane) * 26;
+#pragma unroll
+      for (int c = 0; c < 26; ++c) dst[c] = racc[c];
+    }
+  } else if (warp >= 8 && warp < 12) {
+    // ================= dcT side: TMA producer (lane 0 of warp 8), split of the landed tile ===========
+    const int lw = warp - 8;
+    for (int k = 0; k < my_tiles + kAhead; ++k) {
+      CNN_PHASE(0);
+      if (k >= kAhead) {
+        const int kk = k - kAhead, s = kk % kGtStages;
+        mbar_wait_bounded(&bars.landed[s], (unsigned)(kk / kGtStages) & 1u, status, gave_up);
+        CNN_PHASE(1);
+        if (PASSES == 3) {
+          // element-wise, so the swizzle does not matter: 16-byte piece i of the tile, high part in place,
+          // remainder at the same offset of the low tile; positions past the image hold the TMA's zeros
+          unsigned char* st = stage0 + s * kGtStageBytes;
+          constexpr int kMine = (int)(kABytes / 16) / 128;
+          float4 v[kMine];
+#pragma unroll
+          for (int i = 0; i < kMine; ++i)
+            v[i] = *reinterpret_cast<const float4*>(st + (unsigned)(lw * 32 + lane + 128 * i) * 16u);
+#pragma unroll
+          for (int i = 0; i < kMine; ++i) {
+            unsigned char* p = st + (unsigned)(lw * 32 + lane + 128 * i) * 16u;
+            float4 hi, lo;
+            tc::split_tf32(v[i].x, hi.x, lo.x); tc::split_tf32(v[i].y, hi.y, lo.y);
+            tc::split_tf32(v[i].z, hi.z, lo.z); tc::split_tf32(v[i].w, hi.w, lo.w);
+            *reinterpret_cast<float4*>(p) = hi;
+            *reinterpret_cast<float4*>(p + kLoOff) = lo;
+          }
+          tc::fence_async_smem();    // generic-proxy writes -> visible to the tensor core's operand reads
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.full[s]);
+        CNN_PHASE(2);
+      }
+      if (k < my_tiles && warp == 8) {
+        const int s = k % kGtStages;
+        mbar_wait_bounded(&bars.free[s], ((unsigned)(k / kGtStages) & 1u) ^ 1u, status, gave_up);
+        CNN_PHASE(3);
+        if (lane == 0) {
+          long b;
+          int pos0;
+          tile_origin(k, b, pos0);
+          // the stage's previous readers were the tensor core (async proxy) and, in the three-pass mode,
+          // generic-proxy splits that completed before its MMAs: nothing else to order here
+          mbar_expect_tx(&bars.landed[s], kABytes);
+#pragma unroll
+          for (int kb = 0; kb < TP / 32; ++kb)
+            tma_load_3d(stage0 + s * kGtStageBytes + kb * kGtKBlock, &dc_map, pos0 + 32 * kb, 0, (int)b, &bars.landed[s]);
+        }
+        __syncwarp();
+      }
+      CNN_PHASE(4);
+    }
+  } else {
+    // ================= im2colT side: warps 1-3 and 12 ================================================
+    const int lw = warp < 4 ? warp - 1 : 3;
+    // lane = 4 * (tap within its group of 8) + (position within the chunk)
+    int tap_off[4];
+    bool tap_live[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int t = 8 * g + (lane >> 2);
+      tap_live[g] = t < 25;
+      tap_off[g] = tap_live[g] ? (t / 5) * d.H + (t % 5) + (lane & 3) : 0;
+    }
+    constexpr int kBAhead = kGtStages - 2;
+    for (int k = 0; k < my_tiles + kBAhead; ++k) {
+      CNN_PHASE(0);
+      if (k >= kBAhead) {
+        const int kk = k - kBAhead, s = kk % kGtStages;
+        cp_async_wait<kBAhead - 1>();
+        CNN_PHASE(1);
+        if (PASSES == 3) {
+          unsigned char* st = stage0 + s * kGtStageBytes + kABytes;
+          long b;
+          int pos0;
+          tile_origin(kk, b, pos0);
+          constexpr int kMine = CH / 4;
+          float v[kMine][4];
+#pragma unroll
+          for (int j = 0; j < kMine; ++j)
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              v[j][g] = *reinterpret_cast<const float*>(st + g * kGroup + (unsigned)(lw + 4 * j) * 128u + (unsigned)lane * 4u);
+#pragma unroll
+          for (int j = 0; j < kMine; ++j) {
+            const int c = lw + 4 * j;
+            if (pos0 + 4 * c < CC) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (tap_live[g]) {
+                  unsigned char* p = st + g * kGroup + (unsigned)c * 128u + (unsigned)lane * 4u;
+                  float hi, lo;
+                  tc::split_tf32(v[j][g], hi, lo);
+                  *reinterpret_cast<float*>(p) = hi;
+                  *reinterpret_cast<float*>(p + kLoOff) = lo;
+                }
+              }
+            }
+          }
+        }
+        tc::fence_async_smem();    // generic-proxy writes -> visible to the tensor core's operand reads
+        __syncwarp();              // ... every lane's, before the warp's one arrival
+        if (lane == 0) mbar_arrive(&bars.full[s]);
+        CNN_PHASE(2);
+      }
+      if (k < my_tiles) {
+        const int s = k % kGtStages;
+        mbar_wait_bounded(&bars.free[s], ((unsigned)(k / kGtStages) & 1u) ^ 1u, status, gave_up);
+        CNN_PHASE(3);
+        unsigned char* st = stage0 + s * kGtStageBytes + kABytes;
+        long b;
+        int pos0;
+        tile_origin(k, b, pos0);
+        const float* img = images + (size_t)b * d.H * d.H;
+        // chunk c = lw + 4 j (four consecutive positions of one output row); for each, the four tap groups.
+        // Chunks past the image keep what the stage held (finite; their dc is zero).
+#pragma unroll 2
+        for (int c = lw; c < CH; c += 4) {
+          const int pos = pos0 + 4 * c;
+          if (pos < CC) {
+            const int y = pos / d.C, x = pos - y * d.C;
+            const float* src = img + y * d.H + x;
+            unsigned char* dst = st + (unsigned)c * 128u + (unsigned)lane * 4u;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              if (tap_live[g]) cp_async4(dst + g * kGroup, src + tap_off[g]);
+          }
+        }
+      }
+      cp_async_commit();       // (an empty group past the last tile keeps the count uniform)
+      CNN_PHASE(4);
+    }
+  }
+
+  CNN_PHASE_END(g_phase_clocks_wg);
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem_d, 64);
+}
+
+// The tensor map over dc [cap images][F maps][CC positions] as (position, map, image); box = 32 positions x
+// 64 maps with the 128-byte swizzle = one K-block of the dcT operand.
+static int encode_dc_map(cnn_wide* w) {
+  if (w->dc_map_ptr == w->dc && w->dc_map_cap == w->cap) return CNN_OK;
+  typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static encode_fn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CNN_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !fn) {
+      set_error("cuTensorMapEncodeTiled is not available from this driver");
+      return CNN_ERR_CUDA;
+    }
+    encode = reinterpret_cast<encode_fn>(fn);
+  }
+  const WideDims& d = w->d;
+  const cuuint64_t CC = (cuuint64_t)d.C * d.C;
+  const cuuint64_t dims[3] = {CC, (cuuint64_t)kGtF, (cuuint64_t)w->cap};
+  const cuuint64_t strides[2] = {CC * 4, (cuuint64_t)kGtF * CC * 4};     // bytes, for dimensions 1 and 2
+  const cuuint32_t box[3] = {32, (cuuint32_t)kGtF, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = encode(reinterpret_cast<CUtensorMap*>(w->dc_map), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, w->dc, dims, strides,
+                      box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with %d", (int)r);
+    return CNN_ERR_CUDA;
+  }
+  w->dc_map_ptr = w->dc;
+  w->dc_map_cap = w->cap;
+  return CNN_OK;
+}
+
+bool wide_grad_tc_supported(const WideDims& d) { return d.F == kGtF && d.C % 4 == 0; }
+
+int wide_grad_c1_tc(cnn_wide* w, const float* d_images, long n, int* rows_out, cudaStream_t st) {
+  const WideDims& d = w->d;
+  const size_t smem = (size_t)kGtStages * kGtStageBytes + sizeof(GtBarriers) + 1024;
+  const bool three = (w->conv_mode == 2);
+  const int tp = three ? 64 : 128;
+  const long n_tiles = n * ((d.C * d.C + tp - 1) / tp);
+  long grid = sm_count();
+  if (grid > n_tiles) grid = n_tiles;
+  if (grid > w->part_rows) grid = w->part_rows;
+  int rc = encode_dc_map(w);
+  if (rc != CNN_OK) return rc;
+  const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(w->dc_map);
+  if (three) {
+    CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1_pipe<64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_wide_grad_c1_pipe<64, 3><<<(unsigned)grid, kGtThreads, smem, st>>>(d, map, d_images, n, w->part_c, w->d_status);
+  } else {
+    CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1_pipe<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_wide_grad_c1_pipe<128, 1><<<(unsigned)grid, kGtThreads, smem, st>>>(d, map, d_images, n, w->part_c, w->d_status);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "k_wide_grad_c1_pipe launch");
+  *rows_out = (int)grid;
+  return CNN_OK;
+}
+
+}  // namespace cnn
+
+#ifdef CNN_PHASE_CLOCKS
+// Sums of the SM clock at each stamp for the 13 warps of CTA 0 of the last launch (tuning builds only).
+extern "C" int cnn_debug_phase_clocks_wg(long long* out /* [13][16] */) {
+  return cudaMemcpyFromSymbol(out, cnn::g_phase_clocks_wg, sizeof(cnn::g_phase_clocks_wg)) == cudaSuccess ? 0 : 2;
+}
+#endif
