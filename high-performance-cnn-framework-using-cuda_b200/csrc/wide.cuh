@@ -28,6 +28,7 @@ struct cnn_wide {
   long cap = 0;                 // images the workspace holds
   float *ac = nullptr, *dc = nullptr, *as = nullptr, *ds = nullptr, *delta_f = nullptr, *err = nullptr;
   float *part_c = nullptr, *part_s = nullptr;
+  float* img_shift = nullptr;   // [cap][4][H][H]: every image shifted left by 0..3 columns (16-byte aligned tap windows)
   float* part_f = nullptr;      // FC weight-gradient partials of the batch slices
   int flavour = 2;              // sigmoid flavour, as cnn_net
   int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)

@@ -20,9 +20,13 @@
 //     4,000 cycles to get into the load/store pipeline -- and a tensor map that produced the
 //     un-swizzled core-matrix layout directly, with 16-byte inner boxes, ran at 2.7 TB/s: the TMA
 //     wants long inner rows.)  No multicast; positions past the image are filled with zeros;
-//   * warps 1-3 and 12 copy the im2colT tile with 4-byte cp.async: a warp instruction covers 8 taps x
-//     4 consecutive positions = one 128-byte core matrix of the operand (conflict-free), read as 8
-//     segments of 16 contiguous bytes of the image (L1/L2-resident);
+//   * warps 1-3 and 12 copy the im2colT tile with 16-byte cp.async.  A tap's window of four
+//     consecutive positions starts at column x + j of an image row, 16-byte aligned only for j = 0
+//     and 4; a small kernel therefore first writes every image shifted left by 0..3 columns, and
+//     tap (i, j) reads the copy shifted by j % 4 at column x + 4 (j / 4).  A warp instruction covers
+//     8 taps x 4 chunks (conflict-free in shared memory, 64 contiguous bytes per tap in global
+//     memory).  (With 4-byte copies straight from the image the 104 gathers of a tile took 3,000
+//     cycles to issue and bound the kernel);
 //   * in the three-pass mode (hi*hi + lo*hi + hi*lo, fp32-level accuracy) warps 8-11 split the dcT
 //     tile in place into a tf32-exact high tile and a remainder tile once it has landed, and the
 //     im2col warps split what they copied; in the one-pass mode the tensor core reads the fp32
@@ -85,7 +89,7 @@ constexpr unsigned kGtKBlock = 64 * 128;   // bytes of one K-block of the dcT op
 // a low tile of each operand).
 template <int TP, int PASSES>
 __global__ void __launch_bounds__(kGtThreads, 1)
-k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap dc_map, const float* __restrict__ images, long n,
+k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap dc_map, const float* __restrict__ shifted, long n,
                     float* __restrict__ part, int* __restrict__ status) {
   constexpr int CH = TP / 4;                          // 16-byte chunks along K
   constexpr unsigned kGroup = tc::tile_group_stride(CH);
@@ -261,16 +265,20 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap dc_map, cons
   } else {
     // ================= im2colT side: warps 1-3 and 12 ================================================
     const int lw = warp < 4 ? warp - 1 : 3;
-    // lane = 4 * (tap within its group of 8) + (position within the chunk)
+    // lane = (tap within its group of 8) + 8 * (chunk within its quad)
+    const int HH = d.H * d.H;
     int tap_off[4];
     bool tap_live[4];
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      const int t = 8 * g + (lane >> 2);
+      const int t = 8 * g + (lane & 7);
       tap_live[g] = t < 25;
-      tap_off[g] = tap_live[g] ? (t / 5) * d.H + (t % 5) + (lane & 3) : 0;
+      const int ti = t / 5, tj = t % 5;
+      tap_off[g] = tap_live[g] ? (tj & 3) * HH + ti * d.H + 4 * (tj >> 2) : 0;   // copy shifted by j % 4, row + i, column + 4 (j / 4)
     }
     constexpr int kBAhead = kGtStages - 2;
+    constexpr int kQuads = CH / 4;                     // chunk quads of a tile; warp lw takes quads lw, lw + 4, ...
+    constexpr int kMine = (kQuads + 3) / 4;
     for (int k = 0; k < my_tiles + kBAhead; ++k) {
       CNN_PHASE(0);
       if (k >= kBAhead) {
@@ -278,29 +286,31 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap dc_map, cons
         cp_async_wait<kBAhead - 1>();
         CNN_PHASE(1);
         if (PASSES == 3) {
+          // split what this lane copied, in place: the high part stays, the remainder goes to the low tile
           unsigned char* st = stage0 + s * kGtStageBytes + kABytes;
           long b;
           int pos0;
           tile_origin(kk, b, pos0);
-          constexpr int kMine = CH / 4;
-          float v[kMine][4];
+          float4 v[kMine][4];
 #pragma unroll
-          for (int j = 0; j < kMine; ++j)
+          for (int q = 0; q < kMine; ++q)
 #pragma unroll
             for (int g = 0; g < 4; ++g)
-              v[j][g] = *reinterpret_cast<const float*>(st + g * kGroup + (unsigned)(lw + 4 * j) * 128u + (unsigned)lane * 4u);
+              v[q][g] = *reinterpret_cast<const float4*>(st + g * kGroup + (unsigned)(4 * (lw + 4 * q) + (lane >> 3)) * 128u +
+                                                         (unsigned)(lane & 7) * 16u);
 #pragma unroll
-          for (int j = 0; j < kMine; ++j) {
-            const int c = lw + 4 * j;
-            if (pos0 + 4 * c < CC) {
+          for (int q = 0; q < kMine; ++q) {
+            const int c = 4 * (lw + 4 * q) + (lane >> 3);
+            if (lw + 4 * q < kQuads && pos0 + 4 * c < CC) {
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 if (tap_live[g]) {
-                  unsigned char* p = st + g * kGroup + (unsigned)c * 128u + (unsigned)lane * 4u;
-                  float hi, lo;
-                  tc::split_tf32(v[j][g], hi, lo);
-                  *reinterpret_cast<float*>(p) = hi;
-                  *reinterpret_cast<float*>(p + kLoOff) = lo;
+                  unsigned char* p = st + g * kGroup + (unsigned)c * 128u + (unsigned)(lane & 7) * 16u;
+                  float4 hi, lo;
+                  tc::split_tf32(v[q][g].x, hi.x, lo.x); tc::split_tf32(v[q][g].y, hi.y, lo.y);
+                  tc::split_tf32(v[q][g].z, hi.z, lo.z); tc::split_tf32(v[q][g].w, hi.w, lo.w);
+                  *reinterpret_cast<float4*>(p) = hi;
+                  *reinterpret_cast<float4*>(p + kLoOff) = lo;
                 }
               }
             }
@@ -319,19 +329,19 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap dc_map, cons
         long b;
         int pos0;
         tile_origin(k, b, pos0);
-        const float* img = images + (size_t)b * d.H * d.H;
-        // chunk c = lw + 4 j (four consecutive positions of one output row); for each, the four tap groups.
+        const float* img = shifted + (size_t)b * 4 * HH;
         // Chunks past the image keep what the stage held (finite; their dc is zero).
-#pragma unroll 2
-        for (int c = lw; c < CH; c += 4) {
+#pragma unroll
+        for (int q = 0; q < kMine; ++q) {
+          const int c = 4 * (lw + 4 * q) + (lane >> 3);
           const int pos = pos0 + 4 * c;
-          if (pos < CC) {
+          if (lw + 4 * q < kQuads && pos < CC) {
             const int y = pos / d.C, x = pos - y * d.C;
             const float* src = img + y * d.H + x;
-            unsigned char* dst = st + (unsigned)c * 128u + (unsigned)lane * 4u;
+            unsigned char* dst = st + (unsigned)c * 128u + (unsigned)(lane & 7) * 16u;
 #pragma unroll
             for (int g = 0; g < 4; ++g)
-              if (tap_live[g]) cp_async4(dst + g * kGroup, src + tap_off[g]);
+              if (tap_live[g]) cp_async16(dst + g * kGroup, src + tap_off[g]);
           }
         }
       }
@@ -344,6 +354,20 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap dc_map, cons
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem_d, 64);
+}
+
+// shifted[b][s][y][x] = image[b][y][x + s] (zero past the row's end), s = 0..3.
+__global__ void k_wide_shift_images(int H, const float* __restrict__ images, long n, float* __restrict__ shifted) {
+  const long total = n * 4 * H * H;
+  for (long o = (long)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (long)gridDim.x * blockDim.x) {
+    const int x = (int)(o % H);
+    const long r = o / H;            // (b * 4 + s) * H + y
+    const int y = (int)(r % H);
+    const long bs = r / H;
+    const int s = (int)(bs & 3);
+    const long b = bs >> 2;
+    shifted[o] = (x + s < H) ? images[(b * H + y) * H + x + s] : 0.f;
+  }
 }
 
 // The tensor map over dc [cap images][F maps][CC positions] as (position, map, image); box = 32 positions x
@@ -382,7 +406,7 @@ static int encode_dc_map(cnn_wide* w) {
   return CNN_OK;
 }
 
-bool wide_grad_tc_supported(const WideDims& d) { return d.F == kGtF && d.C % 4 == 0; }
+bool wide_grad_tc_supported(const WideDims& d) { return d.F == kGtF && d.C % 4 == 0 && d.H % 4 == 0; }
 
 int wide_grad_c1_tc(cnn_wide* w, const float* d_images, long n, int* rows_out, cudaStream_t st) {
   const WideDims& d = w->d;
@@ -396,12 +420,13 @@ int wide_grad_c1_tc(cnn_wide* w, const float* d_images, long n, int* rows_out, c
   int rc = encode_dc_map(w);
   if (rc != CNN_OK) return rc;
   const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(w->dc_map);
+  k_wide_shift_images<<<(unsigned)(4 * sm_count()), 256, 0, st>>>(d.H, d_images, n, w->img_shift);
   if (three) {
     CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1_pipe<64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_wide_grad_c1_pipe<64, 3><<<(unsigned)grid, kGtThreads, smem, st>>>(d, map, d_images, n, w->part_c, w->d_status);
+    k_wide_grad_c1_pipe<64, 3><<<(unsigned)grid, kGtThreads, smem, st>>>(d, map, w->img_shift, n, w->part_c, w->d_status);
   } else {
     CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1_pipe<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_wide_grad_c1_pipe<128, 1><<<(unsigned)grid, kGtThreads, smem, st>>>(d, map, d_images, n, w->part_c, w->d_status);
+    k_wide_grad_c1_pipe<128, 1><<<(unsigned)grid, kGtThreads, smem, st>>>(d, map, w->img_shift, n, w->part_c, w->d_status);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_wide_grad_c1_pipe launch");
