@@ -288,7 +288,7 @@ k_wide_grad_c1(WideDims d, const float* __restrict__ images, const float* __rest
 // are combined by a fixed shuffle tree (the same order every run).  (One thread per value walking up
 // to 1,024 rows took 79 us of a 1.3 ms step.)
 __global__ void __launch_bounds__(256)
-k_wide_reduce(WideDims d, long n, long rows_c, const float* __restrict__ part_c,
+k_wide_reduce(WideDims d, long n, long rows_c, long rows_s, const float* __restrict__ part_c,
               const float* __restrict__ part_s, const float* __restrict__ err, float* __restrict__ G) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -297,7 +297,7 @@ k_wide_reduce(WideDims d, long n, long rows_c, const float* __restrict__ part_c,
   const float* src;
   long rows, stride;
   if (t < n_c) { src = part_c + t; rows = rows_c; stride = n_c; }
-  else if (t < n_c + 17) { src = part_s + (t - n_c); rows = n; stride = 17; }
+  else if (t < n_c + 17) { src = part_s + (t - n_c); rows = rows_s; stride = 17; }
   else { src = err; rows = n; stride = 1; }
   float sum = 0.f;
   for (long b = lane; b < rows; b += 32) sum += src[(size_t)b * stride];
@@ -341,7 +341,7 @@ static int wide_reserve(cnn_wide* w, long n) {
   CNN_CUDA(cudaMalloc(&w->err, sizeof(float) * n));
   w->part_rows = n > 4096 ? n : 4096;
   CNN_CUDA(cudaMalloc(&w->part_c, sizeof(float) * (size_t)d.F * 26 * w->part_rows));
-  CNN_CUDA(cudaMalloc(&w->part_s, sizeof(float) * 17 * n));
+  CNN_CUDA(cudaMalloc(&w->part_s, sizeof(float) * 17 * w->part_rows));   // one row per image, or per CTA of the fused kernel
   if (wide_grad_tc_supported(d)) CNN_CUDA(cudaMalloc(&w->img_shift, sizeof(float) * 4 * (size_t)d.H * d.H * n));
   if (!w->part_f) CNN_CUDA(cudaMalloc(&w->part_f, sizeof(float) * (size_t)kWideFcSplit * kOut * d.S));
   w->cap = n;
@@ -481,19 +481,20 @@ int cnn_wide_grad_batch(cnn_wide* w, const float* d_images, const unsigned int* 
   k_wide_bp_s1<<<(unsigned)((ns + 255) / 256), 256, 0, st>>>(d, n, w->as, w->delta_f, w->d_params, w->ds);
   k_wide_grad_fc<<<dim3((d.S + 127) / 128, kWideFcSplit), 128, 0, st>>>(d, n, w->as, w->delta_f, w->part_f);
   k_wide_grad_fc_sum<<<(unsigned)(((long)kOut * d.S + 255) / 256), 256, 0, st>>>(d, n, w->part_f, w->delta_f, d_grad);
-  k_wide_bp_c1<<<(unsigned)n, 256, 0, st>>>(d, w->ac, w->ds, w->d_params, w->dc, w->part_s);
-  const size_t smem = sizeof(float) * ((size_t)d.H * d.H + 8 * kWideGg * 26);
-  CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  long rows_c = n;
+  long rows_c = n, rows_s = n;
   if (w->conv_mode > 0 && wide_grad_tc_supported(d)) {
+    // conv deltas, conv weight gradient and subsample-filter gradient in one kernel; the deltas stay on chip
     int rows = 0;
     if ((rc = wide_grad_c1_tc(w, d_images, n, &rows, st)) != CNN_OK) return rc;
-    rows_c = rows;
+    rows_c = rows_s = rows;
   } else {
+    k_wide_bp_c1<<<(unsigned)n, 256, 0, st>>>(d, w->ac, w->ds, w->d_params, w->dc, w->part_s);
+    const size_t smem = sizeof(float) * ((size_t)d.H * d.H + 8 * kWideGg * 26);
+    CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_wide_grad_c1<<<dim3((unsigned)n, (d.F + kWideGg - 1) / kWideGg), 256, smem, st>>>(d, d_images, w->dc, w->part_c);
   }
   const int n_red = d.F * 26 + 18;       // one warp each
-  k_wide_reduce<<<(n_red + 7) / 8, 256, 0, st>>>(d, n, rows_c, w->part_c, w->part_s, w->err, d_grad);
+  k_wide_reduce<<<(n_red + 7) / 8, 256, 0, st>>>(d, n, rows_c, rows_s, w->part_c, w->part_s, w->err, d_grad);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "wide backward launch");
   return CNN_OK;

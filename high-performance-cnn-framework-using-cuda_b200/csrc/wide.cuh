@@ -34,11 +34,11 @@ struct cnn_wide {
   int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)
   int* d_status = nullptr;      // bounded-wait status word
   long part_rows = 0;           // rows of [F][26] that part_c holds
-  // Tensor map (a CUtensorMap, kept opaque here) through which the weight-gradient kernel reads dc, and what it
-  // was encoded for.
-  alignas(64) unsigned char dc_map[128] = {};
-  const float* dc_map_ptr = nullptr;
-  long dc_map_cap = 0;
+  // Tensor map (a CUtensorMap, kept opaque here) through which the fused delta + weight-gradient kernel reads the
+  // conv activations, and what it was encoded for.
+  alignas(64) unsigned char ac_map[128] = {};
+  const float* ac_map_ptr = nullptr;
+  long ac_map_cap = 0;
 };
 
 
@@ -47,6 +47,7 @@ bool wide_conv_tc_supported(const WideDims& d);
 // Conv + bias + sigmoid on the tensor cores: writes w->ac for n images.
 int wide_conv_fwd_tc(cnn_wide* w, const float* d_images, long n, cudaStream_t st);
 bool wide_grad_tc_supported(const WideDims& d);
-// Conv weight + bias gradient partials on the tensor cores: fills w->part_c with *rows_out rows of [F][26].
+// Conv deltas, conv weight + bias gradient partials and subsample-filter gradient partials on the tensor cores,
+// from w->ac and w->ds: fills w->part_c with *rows_out rows of [F][26] and w->part_s with as many rows of [17].
 int wide_grad_c1_tc(cnn_wide* w, const float* d_images, long n, int* rows_out, cudaStream_t st);
 }  // namespace cnn
