@@ -454,18 +454,26 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
   }
 }
 
-// shifted[b][s][y][x] = image[b][y][x + s] (zero past the row's end), s = 0..3.
-__global__ void k_wide_shift_images(int H, const float* __restrict__ images, long n, float* __restrict__ shifted) {
-  const long total = n * 4 * H * H;
-  for (long o = (long)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (long)gridDim.x * blockDim.x) {
-    const int x = (int)(o % H);
-    const long r = o / H;            // (b * 4 + s) * H + y
-    const int y = (int)(r % H);
-    const long bs = r / H;
-    const int s = (int)(bs & 3);
-    const long b = bs >> 2;
-    shifted[o] = (x + s < H) ? images[(b * H + y) * H + x + s] : 0.f;
-  }
+// shifted[b][s][y][x] = image[b][y][x + s] (zero past the row's end), s = 0..3.  One thread per four
+// consecutive output columns.
+__global__ void __launch_bounds__(256)
+k_wide_shift_images(int H, const float* __restrict__ images, long n, float* __restrict__ shifted) {
+  const int q = H >> 2;                                   // float4 groups per row
+  const long total = n * 4 * H * q;
+  const long o = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= total) return;
+  const int x = 4 * (int)(o % q);
+  const long r = o / q;                                   // (b * 4 + s) * H + y
+  const int y = (int)(r % H);
+  const long bs = r / H;
+  const int s = (int)(bs & 3);
+  const float* src = images + ((bs >> 2) * H + y) * H;
+  float4 v;
+  v.x = (x + s < H) ? src[x + s] : 0.f;
+  v.y = (x + 1 + s < H) ? src[x + 1 + s] : 0.f;
+  v.z = (x + 2 + s < H) ? src[x + 2 + s] : 0.f;
+  v.w = (x + 3 + s < H) ? src[x + 3 + s] : 0.f;
+  reinterpret_cast<float4*>(shifted)[o] = v;
 }
 
 // The tensor map over the conv activations [cap images][F maps][CC positions] as (position, map, image);
@@ -520,7 +528,7 @@ int wide_grad_c1_tc(cnn_wide* w, const float* d_images, long n, int* rows_out, c
   int rc = encode_ac_map(w);
   if (rc != CNN_OK) return rc;
   const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(w->ac_map);
-  k_wide_shift_images<<<(unsigned)(4 * sm_count()), 256, 0, st>>>(d.H, d_images, n, w->img_shift);
+  k_wide_shift_images<<<(unsigned)((n * d.H * d.H + 255) / 256), 256, 0, st>>>(d.H, d_images, n, w->img_shift);
 #define CNN_LAUNCH_PIPE(TPV, PV)                                                                                     \
   do {                                                                                                               \
     CNN_CUDA(cudaFuncSetAttribute(k_wide_grad_c1_pipe<TPV, PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
