@@ -149,18 +149,37 @@ k_wide_fc_fwd(WideDims d, long n, const float* __restrict__ as, const float* __r
 }
 
 // ---- backward --------------------------------------------------------------------------------
-// delta_s[b][s] = (sum_k Wf[k][s] delta_f[b][k]) * as (1 - as)
-__global__ void k_wide_bp_s1(WideDims d, long n, const float* __restrict__ as, const float* __restrict__ delta_f,
-                             const float* __restrict__ params, float* __restrict__ ds) {
-  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= n * d.S) return;
-  const long b = idx / d.S;
-  const int s = (int)(idx % d.S);
-  float acc = 0.f;
+// delta_s[b][s] = (sum_k Wf[k][s] delta_f[b][k]) * as (1 - as).  Thread = one s for kWideBpImgs images: the ten
+// weights of s stay in registers, the images' output deltas come from shared memory.
+constexpr int kWideBpImgs = 8;
+
+__global__ void __launch_bounds__(256)
+k_wide_bp_s1(WideDims d, long n, const float* __restrict__ as, const float* __restrict__ delta_f,
+             const float* __restrict__ params, float* __restrict__ ds) {
+  __shared__ float dlt[kWideBpImgs][kOut];
+  const long b0 = (long)blockIdx.x * kWideBpImgs;     // images along x (no 65,535 limit), the S range along y
+  const int imgs = (int)((n - b0) < kWideBpImgs ? (n - b0) : kWideBpImgs);
+  if (threadIdx.x < kWideBpImgs * kOut) {
+    const int g = threadIdx.x / kOut, k = threadIdx.x % kOut;
+    dlt[g][k] = (g < imgs) ? delta_f[(b0 + g) * kOut + k] : 0.f;
+  }
+  __syncthreads();
+  const int s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (s >= d.S) return;
+  float wv[kOut];
 #pragma unroll
-  for (int k = 0; k < kOut; ++k) acc = fmaf(params[d.o_wf + (size_t)k * d.S + s], delta_f[b * kOut + k], acc);
-  const float a = as[idx];
-  ds[idx] = acc * a * (1.f - a);
+  for (int k = 0; k < kOut; ++k) wv[k] = params[d.o_wf + (size_t)k * d.S + s];
+#pragma unroll
+  for (int g = 0; g < kWideBpImgs; ++g) {
+    if (g < imgs) {
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) acc = fmaf(wv[k], dlt[g][k], acc);
+      const size_t idx = (size_t)(b0 + g) * d.S + s;
+      const float a = as[idx];
+      ds[idx] = acc * a * (1.f - a);
+    }
+  }
 }
 
 // G_wf[k][s] = sum_b delta_f[b][k] as[b][s].  The batch is cut into kWideFcSplit contiguous slices
@@ -506,8 +525,8 @@ int cnn_wide_grad_batch(cnn_wide* w, const float* d_images, const unsigned int* 
   int rc = wide_reserve(w, n);
   if (rc != CNN_OK) return rc;
   if ((rc = wide_forward_dispatch(w, d_images, d_labels, n, nullptr, nullptr, true, st)) != CNN_OK) return rc;
-  const long ns = n * d.S;
-  k_wide_bp_s1<<<(unsigned)((ns + 255) / 256), 256, 0, st>>>(d, n, w->as, w->delta_f, w->d_params, w->ds);
+  k_wide_bp_s1<<<dim3((unsigned)((n + kWideBpImgs - 1) / kWideBpImgs), (unsigned)((d.S + 255) / 256)), 256, 0, st>>>(
+      d, n, w->as, w->delta_f, w->d_params, w->ds);
   k_wide_grad_fc<<<dim3((d.S + 127) / 128, kWideFcSplit), 128, 0, st>>>(d, n, w->as, w->delta_f, w->part_f);
   k_wide_grad_fc_sum<<<(unsigned)(((long)kOut * d.S + 255) / 256), 256, 0, st>>>(d, n, w->part_f, w->delta_f, d_grad);
   long rows_c = n, rows_s = n;
