@@ -30,7 +30,7 @@ struct cnn_wide {
   float *part_c = nullptr, *part_s = nullptr;
   float* img_shift = nullptr;   // [cap][4][H][H]: every image shifted left by 0..3 columns (16-byte aligned tap windows)
   float* part_f = nullptr;      // FC weight-gradient partials of the batch slices
-  int flavour = 2;              // sigmoid flavour, as cnn_net
+  int flavour = 1;              // sigmoid flavour (cnn_common.cuh): 1 = the short form (default, as cnn_net), 2 = refined, 0 = reference expression
   int conv_mode = 0;            // 0 fp32 SIMT, 1 tf32 tcgen05 (one pass), 2 tf32 tcgen05 (three passes)
   int* d_status = nullptr;      // bounded-wait status word
   long part_rows = 0;           // rows of [F][26] that part_c holds

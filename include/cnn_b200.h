@@ -306,9 +306,12 @@ int cnn_wide_create(int H, int F, cnn_wide** out);       /* parameters start at 
 int cnn_wide_destroy(cnn_wide* w);
 int cnn_wide_set_params(cnn_wide* w, const float* h_params);
 int cnn_wide_get_params(cnn_wide* w, float* h_params);
-/* "fast_sigmoid" 0 / 1 / 2 as for cnn_net; "conv": 0 = fp32 SIMT convolution, 1 = implicit GEMM on the
- * tf32 tensor cores (tcgen05, about 1e-3 relative), 2 = the same in three tf32 passes (hi*hi + lo*hi +
- * hi*lo, fp32-level accuracy).  Tensor-core modes need F to be a multiple of 16, at most 256. */
+/* "fast_sigmoid": 0 = the reference's expression, 1 = the short form (default, as for cnn_net), 2 = a
+ * refined form (two-step argument reduction, Newton-refined reciprocal); "conv": 0 = fp32 SIMT
+ * convolution, 1 = implicit GEMM on the tf32 tensor cores (tcgen05, about 1e-3 relative), 2 = the same
+ * in three tf32 passes (hi*hi + lo*hi + hi*lo, fp32-level accuracy).  The tensor-core forward needs F to
+ * be a multiple of 16, at most 256; the fused tensor-core backward (conv deltas + weight gradients in one
+ * TMA-fed kernel) needs F = 64 and H a multiple of 4, otherwise the fp32 SIMT backward runs. */
 int cnn_wide_set_option(cnn_wide* w, const char* key, int value);
 /* As cnn_net_status. */
 int cnn_wide_status(cnn_wide* w, int* status);
