@@ -21,10 +21,9 @@
 //     stored per (image, map) with positions contiguous, a 3-D tensor map (position, map, image) with a box of
 //     32 positions x 64 maps and the 128-byte swizzle writes one K-block of the operand (64 rows of
 //     128 bytes) per cp.async.bulk.tensor, and the MMA reads it through a SWIZZLE_128B descriptor.
-//     (Copying the tile with per-thread cp.async stalled at 2 TB/s -- the copies of one tile took
-//     4,000 cycles to get into the load/store pipeline -- and a tensor map that produced the
-//     un-swizzled core-matrix layout directly, with 16-byte inner boxes, ran at 2.7 TB/s: the TMA
-//     wants long inner rows.)  No multicast; positions past the image are filled with zeros;
+//     (Copying the tile with per-thread cp.async stalled at 2 TB/s: the copies of one tile took
+//     4,000 cycles to get into the load/store pipeline.)  No multicast; positions past the image
+//     are filled with zeros;
 //   * warps 1-3 copy the im2colT tile with 16-byte cp.async.  A tap's window of four
 //     consecutive positions starts at column x + j of an image row, 16-byte aligned only for j = 0
 //     and 4; a small kernel therefore first writes every image shifted left by 0..3 columns, and
