@@ -107,7 +107,15 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
   constexpr unsigned kGroup = tc::tile_group_stride(CH);
   constexpr unsigned kABytes = (kGtF / 8) * kGroup;   // TP * 256
   constexpr unsigned kBBytes = 4 * kGroup;            // 32 tap rows: TP * 128
-  constexpr unsigned kLoOff = kABytes + kBBytes;      // low tiles behind the high ones
+  // Stage layout: [delta tile | its low part (three passes) | im2col tile | its low part].  With three passes
+  // the two im2col tiles lie back to back and are read as ONE operand of 64 rows: the high delta tile times
+  // [hi taps | lo taps] fills 64 accumulator columns in one MMA per K step (hi*hi in columns 0..31, hi*lo in
+  // 32..63), the low delta tile times the hi taps adds lo*hi to columns 0..31 -- two MMAs per K step instead
+  // of three; the flush adds the two column groups.
+  constexpr unsigned kALoOff = kABytes;                                  // low delta tile
+  constexpr unsigned kBOff = (PASSES == 3 ? 2u : 1u) * kABytes;           // im2col tile (high part)
+  constexpr unsigned kBLoOff = kBBytes;                                  // its low part, relative to the high part
+  constexpr unsigned kAccCols = (PASSES == 3) ? 64u : 32u;                // TMEM columns per accumulator
   constexpr int kGtStageBytes = (PASSES == 3 ? 2 : 1) * (int)(kABytes + kBBytes);   // 48 KB at TP = 128 (64 with three passes)
   constexpr int kGtStages = kGtRingBytes / kGtStageBytes;
   static_assert(kGtStages >= 3 && kGtStages <= kGtMaxStages && kGtStageBytes % 1024 == 0, "stage ring");
@@ -130,7 +138,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
   __syncthreads();
   for (int i = tid; i < kGtStages * TP; i += kGtThreads) {
     const int s = i / TP, p = i % TP;
-    *reinterpret_cast<float*>(stage0 + s * kGtStageBytes + kABytes + tc::tile_offset(25, p >> 2, CH) + (p & 3) * 4) = 1.0f;
+    *reinterpret_cast<float*>(stage0 + s * kGtStageBytes + kBOff + tc::tile_offset(25, p >> 2, CH) + (p & 3) * 4) = 1.0f;
   }
   if (tid < 16) bars.ws[tid] = params[d.o_ws + tid];
   if (tid == 0) {
@@ -145,7 +153,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
     }
     mbar_fence_init();
   }
-  if (warp == 0) tc::tmem_alloc(&bars.tmem_base, 64);
+  if (warp == 0) tc::tmem_alloc(&bars.tmem_base, 2 * kAccCols);
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -165,7 +173,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
 
   if (warp == 0) {
     // ================= MMA issue ====================================================================
-    const unsigned idesc = tc::idesc_tf32(kGtF, 32, 0, 0);
+    const unsigned idesc32 = tc::idesc_tf32(kGtF, 32, 0, 0), idesc64 = tc::idesc_tf32(kGtF, 64, 0, 0);
     for (int k = 0; k < my_tiles; ++k) {
       const int s = k % kGtStages;
       const int grp = k / kFlushTiles, acc = grp & 1;
@@ -178,16 +186,20 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
       __syncwarp();
       tc::fence_after_sync();
       const unsigned base = smem_u32(stage0 + s * kGtStageBytes);
+      const unsigned d_acc = tmem_d + (unsigned)acc * kAccCols;
       unsigned accumulate = first ? 0u : 1u;
+      // pass 0: high delta tile x (all im2col rows: 32, or 64 = [hi | lo]); pass 1 (three-pass mode): low delta
+      // tile x hi taps, into the first 32 columns
 #pragma unroll 1
-      for (int pass = 0; pass < PASSES; ++pass) {
-        const unsigned a_s = base + ((pass == 1) ? kLoOff : 0u);
-        const unsigned b_s = base + kABytes + ((pass == 2) ? kLoOff : 0u);
+      for (int pass = 0; pass < (PASSES == 3 ? 2 : 1); ++pass) {
+        const unsigned a_s = base + ((pass == 1) ? kALoOff : 0u);
+        const unsigned b_s = base + kBOff;
+        const unsigned idesc = (PASSES == 3 && pass == 0) ? idesc64 : idesc32;
 #pragma unroll
         for (int ks = 0; ks < TP / 8; ++ks) {          // 8 positions per MMA = two 16-byte chunks
           const unsigned long long ad = smem_desc_sw128(a_s + (unsigned)(ks >> 2) * kGtKBlock + (unsigned)(ks & 3) * 32u);
           const unsigned long long bd = tc::smem_desc(b_s + ks * 256, 128, kGroup);
-          tc::mma_tf32_elect(tmem_d + (unsigned)(acc * 32), ad, bd, idesc, accumulate);
+          tc::mma_tf32_elect(d_acc, ad, bd, idesc, accumulate);
           accumulate = 1;
         }
       }
@@ -208,11 +220,11 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
       CNN_PHASE(1);
       tc::fence_after_sync();
 #pragma unroll
-      for (int c0 = 0; c0 < 32; c0 += 16) {
+      for (int c0 = 0; c0 < (int)kAccCols; c0 += 16) {     // columns 32..63 (three passes) hold hi*lo of the same taps
         float v[16];
-        tc::tmem_ld16(lane_base + (unsigned)(acc * 32 + c0), v);
+        tc::tmem_ld16(lane_base + (unsigned)acc * kAccCols + (unsigned)c0, v);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) racc[c0 + e] += v[e];
+        for (int e = 0; e < 16; ++e) racc[(c0 & 31) + e] += v[e];
       }
       tc::fence_before_sync();
       __syncwarp();
@@ -314,7 +326,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
               tc::split_tf32(dv.x, hi.x, lo.x); tc::split_tf32(dv.y, hi.y, lo.y);
               tc::split_tf32(dv.z, hi.z, lo.z); tc::split_tf32(dv.w, hi.w, lo.w);
               *reinterpret_cast<float4*>(p) = hi;
-              *reinterpret_cast<float4*>(p + kLoOff) = lo;
+              *reinterpret_cast<float4*>(p + kALoOff) = lo;
             } else {
               *reinterpret_cast<float4*>(p) = dv;
             }
@@ -378,7 +390,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
         CNN_PHASE(1);
         if (PASSES == 3) {
           // split what this lane copied, in place: the high part stays, the remainder goes to the low tile
-          unsigned char* st = stage0 + s * kGtStageBytes + kABytes;
+          unsigned char* st = stage0 + s * kGtStageBytes + kBOff;
           long b;
           int pos0;
           tile_origin(kk, b, pos0);
@@ -401,7 +413,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
                   tc::split_tf32(v[q][g].x, hi.x, lo.x); tc::split_tf32(v[q][g].y, hi.y, lo.y);
                   tc::split_tf32(v[q][g].z, hi.z, lo.z); tc::split_tf32(v[q][g].w, hi.w, lo.w);
                   *reinterpret_cast<float4*>(p) = hi;
-                  *reinterpret_cast<float4*>(p + kLoOff) = lo;
+                  *reinterpret_cast<float4*>(p + kBLoOff) = lo;
                 }
               }
             }
@@ -416,7 +428,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
         const int s = k % kGtStages;
         mbar_wait_bounded(&bars.free[s], ((unsigned)(k / kGtStages) & 1u) ^ 1u, status, gave_up);
         CNN_PHASE(3);
-        unsigned char* st = stage0 + s * kGtStageBytes + kABytes;
+        unsigned char* st = stage0 + s * kGtStageBytes + kBOff;
         long b;
         int pos0;
         tile_origin(k, b, pos0);
@@ -444,7 +456,7 @@ k_wide_grad_c1_pipe(WideDims d, const __grid_constant__ CUtensorMap ac_map, cons
   CNN_PHASE_END(g_phase_clocks_wg);
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem_d, 64);
+  if (warp == 0) tc::tmem_dealloc(tmem_d, 2 * kAccCols);
   if (tid < 17) {
     float sum = 0.f;
 #pragma unroll
