@@ -133,3 +133,25 @@ def test_header_is_plain_c(tmp_path):
     r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"),
                         "-fsyntax-only", str(src)], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
+
+
+def test_instrumented_build_exports_the_phase_clock_readers(tmp_path):
+    """`build.py --define CNN_PHASE_CLOCKS --out PATH` (the command the profile summaries give) builds a
+    separate library that exports the clock-stamp readers of the three instrumented kernels; the in-tree
+    library exports none of them."""
+    import importlib.util
+    import shutil
+    if shutil.which("nvcc") is None:
+        pytest.skip("nvcc not available")
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    pkg_dir = [d for d in os.listdir(root) if d.endswith("_b200") and os.path.isdir(os.path.join(root, d))][0]
+    spec = importlib.util.spec_from_file_location("b200_build", os.path.join(root, pkg_dir, "build.py"))
+    build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build)
+    out = str(tmp_path / "libcnn_phase.so")
+    assert build.build_library(defines=("CNN_PHASE_CLOCKS",), out=out) == out
+    lib = ctypes.CDLL(out)
+    plain = ctypes.CDLL(build.build_library())
+    for name in ("cnn_debug_phase_clocks8", "cnn_debug_phase_clocks_tc", "cnn_debug_phase_clocks_wg"):
+        assert hasattr(lib, name), name
+        assert not hasattr(plain, name), name
