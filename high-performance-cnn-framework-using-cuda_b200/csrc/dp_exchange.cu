@@ -70,6 +70,8 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
   // (`mine` is this rank's own buffer, peers.buf[rank], passed separately: the pointer table is a kernel
   // parameter and only compile-time indices keep it out of local memory -- with a 64-byte stack frame
   // for it this kernel took 12 us instead of 6)
+  pdl_launch_dependents();   // the next step's gradient kernel may set itself up now
+  pdl_wait();                // this step's rows are complete
   unsigned seq = 0;
   if (world > 1 && g == 0) seq = mine->step[b] + 1u;   // written only by this block, one launch ago; in flight under the row sums
   float acc = 0.f;
@@ -274,10 +276,10 @@ int cnn_dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels,
   const long long wait_clocks = (long long)dp->wait_limit_ms * dp->clock_khz;
   const int send = dp->drop_next_send ? 0 : 1;
   dp->drop_next_send = 0;
-  k_reduce_exchange_update<<<kDpBlocks, 32 * kDpRedGroups, 0, st>>>(
-      net->d_partials, grid, dp->peers, dp->local, dp->rank, dp->world, net->d_params, scale, d_grad_sum, d_mean_err,
-      err_scale, wait_clocks, send, net->d_status);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(k_reduce_exchange_update, dim3(kDpBlocks), dim3(32 * kDpRedGroups), 0, st,
+                             (const float*)net->d_partials, grid, dp->peers, dp->local, dp->rank, dp->world, net->d_params,
+                             scale, d_grad_sum, d_mean_err, err_scale, wait_clocks, send, net->d_status);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_reduce_exchange_update launch");
   return CNN_OK;
 }

@@ -177,24 +177,26 @@ k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ l
   const int s = live ? tid : kS - 1;
   const int f = s / 36, w = s % 36, p = w / 6, q = w % 6;
 
-  load_params_to_smem(sm, params, tid);
-  if (tid == 0) {
-    mbar_init(&sm.full[0], 1);
-    mbar_init(&sm.full[1], 1);
-    mbar_fence_init();
-  }
-  __syncthreads();
-
+  // In a training loop this kernel follows the previous step's reduce + update kernel.  Launched with
+  // launch_pdl() it starts while that kernel still runs: the barriers and the first two image copies (the
+  // images are nobody's output) are under way when the parameters become readable.
+  pdl_launch_dependents();
   auto issue = [&](int stage, long img) {
     mbar_expect_tx(&sm.full[stage], kImg * sizeof(float));
     bulk_g2s(&sm.img[stage][0], images + img * kImg, kImg * sizeof(float), &sm.full[stage]);
   };
   if (tid == 0) {
+    mbar_init(&sm.full[0], 1);
+    mbar_init(&sm.full[1], 1);
+    mbar_fence_init();
     for (int st = 0; st < 2; ++st) {
       const long im = (long)blockIdx.x + (long)st * gridDim.x;
       if (im < n) issue(st, im);
     }
   }
+  pdl_wait();        // the parameters (and the row buffer this kernel writes at its end) belong to the predecessor until here
+  load_params_to_smem(sm, params, tid);
+  __syncthreads();
 
   float acc_wc[25], acc_ws[16], acc_wf[kOut];
   float acc_bc = 0.f, acc_bs = 0.f, acc_bf = 0.f, acc_err = 0.f;
@@ -316,6 +318,8 @@ k_reduce_rows(const float* __restrict__ rows, int n_rows, float* __restrict__ G,
   __shared__ float part[kRedGroups][33];
   const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + lane;
+  pdl_launch_dependents();   // the next step's gradient kernel may set itself up now
+  pdl_wait();                // the rows are complete
   float acc = 0.f;
   if (col < kRowStride) {
 #pragma unroll 4
@@ -496,21 +500,23 @@ int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_
                                 int grid, cudaStream_t st) {
   const size_t smem = sizeof(TrSmem);
   int rc;
+  cudaError_t le = cudaSuccess;
 #define CNN_LAUNCH_GRAD(FL)                                                                        \
   do {                                                                                             \
     if (grid > sm_count()) {                                                                       \
       if ((rc = set_smem_attr(k_grad_partials<FL, 2>, smem)) != CNN_OK) return rc;                 \
-      k_grad_partials<FL, 2><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params, \
-                                                             net->d_partials, net->d_status);      \
+      le = launch_pdl(k_grad_partials<FL, 2>, dim3(grid), dim3(kTrThreads), smem, st, d_images, d_labels, n, \
+                      (const float*)net->d_params, net->d_partials, net->d_status);                \
     } else {                                                                                       \
       if ((rc = set_smem_attr(k_grad_partials<FL, 1>, smem)) != CNN_OK) return rc;                 \
-      k_grad_partials<FL, 1><<<grid, kTrThreads, smem, st>>>(d_images, d_labels, n, net->d_params, \
-                                                             net->d_partials, net->d_status);      \
+      le = launch_pdl(k_grad_partials<FL, 1>, dim3(grid), dim3(kTrThreads), smem, st, d_images, d_labels, n, \
+                      (const float*)net->d_params, net->d_partials, net->d_status);                \
     }                                                                                              \
   } while (0)
   if (net->fast_sigmoid) CNN_LAUNCH_GRAD(1);
   else CNN_LAUNCH_GRAD(0);
 #undef CNN_LAUNCH_GRAD
+  if (le != cudaSuccess) return cuda_fail(le, "k_grad_partials launch");
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch");
   return CNN_OK;
@@ -581,10 +587,10 @@ int cnn_train_minibatch(cnn_net* net, const float* d_images, const unsigned int*
       const int grid = grid_for_batch(b);
       if ((rc = launch_grad_partials(net, d_images + first * kImg, d_labels + first, b, grid, st)) != CNN_OK)
         return rc;
-      k_reduce_rows<<<(kNParamsPadded + 31) / 32, 32 * kRedGroups, 0, st>>>(
-          net->d_partials, grid, net->d_grad, net->d_params, dt / (float)b,
-          d_mean_err ? d_mean_err + e : nullptr, 1.0f / (float)n);
-      cudaError_t err = cudaGetLastError();
+      cudaError_t err = launch_pdl(k_reduce_rows, dim3((kNParamsPadded + 31) / 32), dim3(32 * kRedGroups), 0, st,
+                                   (const float*)net->d_partials, grid, net->d_grad, net->d_params, dt / (float)b,
+                                   d_mean_err ? d_mean_err + e : nullptr, 1.0f / (float)n);
+      if (err == cudaSuccess) err = cudaGetLastError();
       if (err != cudaSuccess) return cuda_fail(err, "k_reduce_rows launch");
     }
   }

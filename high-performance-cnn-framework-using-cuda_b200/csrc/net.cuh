@@ -57,6 +57,13 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned by
       "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// Programmatic dependent launch: a kernel launched with launch_pdl() may start while its predecessor in the
+// stream is still running, once every block of the predecessor has called pdl_launch_dependents() (or
+// exited); whatever it reads of the predecessor's results must come after pdl_wait(), which returns when
+// the predecessor has completed and its writes are visible.  Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Per-thread asynchronous copies global -> shared (LDGSTS), 16 bytes (L2 only) or 4 bytes, and their groups.
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
