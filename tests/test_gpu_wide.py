@@ -162,7 +162,7 @@ def test_wide_full_batch_matches_oracle(cuda, pkg, ob, mode):
     assert net.status() == 0
     ref_out, ref_arg = ob.forward_batch(params, x, H=H, F=F, threads=0)
     # The FC of this net adds 10,816 products: two fp32 evaluations in different orders already differ
-    # by more than 1e-5 on some of the 10,240 outputs, so the judge here is the fp64 oracle -- 1e-5, or
+    # by more than 1e-5 on some of the 10,240 outputs, so the yardstick here is the fp64 oracle -- 1e-5, or
     # twice the fp32 oracle's own distance from it where that is larger.
     ref64, _ = ob.forward_batch(params, x, H=H, F=F, threads=0, dtype=np.float64)
     e_lib, e_or = rel_err(d_out.cpu().numpy(), ref64), rel_err(ref_out, ref64)
@@ -173,7 +173,7 @@ def test_wide_full_batch_matches_oracle(cuda, pkg, ob, mode):
     print("conv mode %d: %d of %d rows below the 1e-5 argmax margin" % (mode, int((~ok).sum()), n))
     assert np.array_equal(d_arg.cpu().numpy()[ok], ref_arg[ok]) and (~ok).sum() <= 2
     # gradients: sums over 1,024 images (and 2,704 positions for the conv filter) -- the fp64 oracle
-    # judges, with the fp32 oracle's own distance from it as the floor of what fp32 can deliver
+    # is the yardstick, with the fp32 oracle's own distance from it as the floor of what fp32 can deliver
     G, err = ob.grad_batch(params, x, labels, H=H, F=F, threads=0)
     G64, err64 = ob.grad_batch(params, x, labels, H=H, F=F, threads=0, dtype=np.float64)
     g = d_g.cpu().numpy()
