@@ -265,6 +265,35 @@ def test_minibatch_training_matches_oracle(cuda, pkg, ob, params0, n, batch):
     assert np.allclose(d_me.cpu().numpy(), me_or, rtol=1e-5)
 
 
+def test_minibatch_epoch_in_a_cuda_graph_equals_eager(cuda, pkg, params0):
+    """The step's two kernels are launched as programmatic dependents (each may set itself up while its
+    predecessor still runs).  An epoch captured into a CUDA graph and replayed must leave exactly the
+    parameters of the same epoch launched eagerly, and a second replay must continue from there."""
+    n, batch = 2048 + 100, 256
+    images, labels = pkg.synth.synth_images(39, n)
+    d_img, d_lab = to_dev(cuda, images, labels)
+    eager = pkg.Net(0)
+    eager.set_params(params0)
+    eager.train_minibatch(d_img, d_lab, n, batch, 2, 0.1, None)
+    cuda.cuda.synchronize()
+    p_eager = eager.get_params()
+    net = pkg.Net(0)
+    net.set_params(params0)
+    net.train_minibatch(d_img, d_lab, batch, batch, 1, 0.1, None)       # scratch exists before the capture
+    net.set_params(params0)
+    side = cuda.cuda.Stream()
+    with cuda.cuda.stream(side):
+        graph = cuda.cuda.CUDAGraph()
+        with cuda.cuda.graph(graph, stream=side):
+            net.train_minibatch(d_img, d_lab, n, batch, 1, 0.1, None, cuda.cuda.current_stream())
+    cuda.cuda.synchronize()
+    graph.replay()
+    graph.replay()
+    cuda.cuda.synchronize()
+    assert net.status() == 0
+    assert np.array_equal(net.get_params(), p_eager)
+
+
 def test_minibatch_of_one_equals_persample_kernel(cuda, pkg, params0):
     images, labels = pkg.synth.synth_images(38, 50)
     d_img, d_lab = to_dev(cuda, images, labels)
