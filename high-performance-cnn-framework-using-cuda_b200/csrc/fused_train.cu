@@ -166,7 +166,10 @@ __device__ __forceinline__ void thread_backward(const TrSmem& sm, const FwdRegs&
 
 // MINB = 1: one block per SM, no register cap -- lowest latency, used for small batches.
 // MINB = 2: two blocks per SM at 128 registers -- higher throughput on large batches.
-template <int FAST, int MINB>
+// EARLY = true (used when every block has one image: a training step of a few hundred images): the first
+// image copies are issued before the wait for the predecessor kernel.  With many images per block that order
+// of the prologue compiles to a slower loop (1.06 against 0.985 ms for 57,344 images), so it is a variant.
+template <int FAST, int MINB, bool EARLY>
 __global__ void __launch_bounds__(kTrThreads, MINB)
 k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ labels, long n,
                 const float* __restrict__ params, float* __restrict__ rows, int* __restrict__ status) {
@@ -180,23 +183,40 @@ k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ l
   // In a training loop this kernel follows the previous step's reduce + update kernel.  Launched with
   // launch_pdl() it starts while that kernel still runs: the barriers and the first two image copies (the
   // images are nobody's output) are under way when the parameters become readable.
-  pdl_launch_dependents();
   auto issue = [&](int stage, long img) {
     mbar_expect_tx(&sm.full[stage], kImg * sizeof(float));
     bulk_g2s(&sm.img[stage][0], images + img * kImg, kImg * sizeof(float), &sm.full[stage]);
   };
-  if (tid == 0) {
-    mbar_init(&sm.full[0], 1);
-    mbar_init(&sm.full[1], 1);
-    mbar_fence_init();
-    for (int st = 0; st < 2; ++st) {
-      const long im = (long)blockIdx.x + (long)st * gridDim.x;
-      if (im < n) issue(st, im);
+  if (EARLY) {
+    pdl_launch_dependents();   // one short-lived block per image: the reduce kernel's blocks may come on board at once
+    if (tid == 0) {
+      mbar_init(&sm.full[0], 1);
+      mbar_init(&sm.full[1], 1);
+      mbar_fence_init();
+      for (int st = 0; st < 2; ++st) {
+        const long im = (long)blockIdx.x + (long)st * gridDim.x;
+        if (im < n) issue(st, im);
+      }
+    }
+    pdl_wait();      // the parameters (and the row buffer this kernel writes at its end) belong to the predecessor until here
+    load_params_to_smem(sm, params, tid);
+    __syncthreads();
+  } else {
+    pdl_wait();
+    load_params_to_smem(sm, params, tid);
+    if (tid == 0) {
+      mbar_init(&sm.full[0], 1);
+      mbar_init(&sm.full[1], 1);
+      mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid == 0) {
+      for (int st = 0; st < 2; ++st) {
+        const long im = (long)blockIdx.x + (long)st * gridDim.x;
+        if (im < n) issue(st, im);
+      }
     }
   }
-  pdl_wait();        // the parameters (and the row buffer this kernel writes at its end) belong to the predecessor until here
-  load_params_to_smem(sm, params, tid);
-  __syncthreads();
 
   float acc_wc[25], acc_ws[16], acc_wf[kOut];
   float acc_bc = 0.f, acc_bs = 0.f, acc_bf = 0.f, acc_err = 0.f;
@@ -264,6 +284,9 @@ k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ l
     // delta_f only after barrier (A) of the next iteration, which every thread reaches after this
     // point.
   }
+  // With many images per block the reduce kernel is only brought onto the SMs from here on: its blocks wait
+  // for this grid to finish, and while they wait they hold registers that a second gradient block per SM needs.
+  if (!EARLY) pdl_launch_dependents();
 
   // ---- block-level reduction, fixed order ----------------------------------------------------
   float* row = rows + (size_t)blockIdx.x * kRowStride;
@@ -501,21 +524,27 @@ int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_
   const size_t smem = sizeof(TrSmem);
   int rc;
   cudaError_t le = cudaSuccess;
-#define CNN_LAUNCH_GRAD(FL)                                                                        \
-  do {                                                                                             \
-    if (grid > sm_count()) {                                                                       \
-      if ((rc = set_smem_attr(k_grad_partials<FL, 2>, smem)) != CNN_OK) return rc;                 \
-      le = launch_pdl(k_grad_partials<FL, 2>, dim3(grid), dim3(kTrThreads), smem, st, d_images, d_labels, n, \
-                      (const float*)net->d_params, net->d_partials, net->d_status);                \
-    } else {                                                                                       \
-      if ((rc = set_smem_attr(k_grad_partials<FL, 1>, smem)) != CNN_OK) return rc;                 \
-      le = launch_pdl(k_grad_partials<FL, 1>, dim3(grid), dim3(kTrThreads), smem, st, d_images, d_labels, n, \
-                      (const float*)net->d_params, net->d_partials, net->d_status);                \
-    }                                                                                              \
+#define CNN_LAUNCH_GRAD3(FL, MB, EA)                                                                          \
+  do {                                                                                                       \
+    if ((rc = set_smem_attr(k_grad_partials<FL, MB, EA>, smem)) != CNN_OK) return rc;                        \
+    le = launch_pdl(k_grad_partials<FL, MB, EA>, dim3(grid), dim3(kTrThreads), smem, st, d_images, d_labels, n, \
+                    (const float*)net->d_params, net->d_partials, net->d_status);                            \
+  } while (0)
+#define CNN_LAUNCH_GRAD(FL)                                   \
+  do {                                                        \
+    const bool early = ((long)grid == n);                     \
+    if (grid > sm_count()) {                                  \
+      if (early) CNN_LAUNCH_GRAD3(FL, 2, true);               \
+      else CNN_LAUNCH_GRAD3(FL, 2, false);                    \
+    } else {                                                  \
+      if (early) CNN_LAUNCH_GRAD3(FL, 1, true);               \
+      else CNN_LAUNCH_GRAD3(FL, 1, false);                    \
+    }                                                         \
   } while (0)
   if (net->fast_sigmoid) CNN_LAUNCH_GRAD(1);
   else CNN_LAUNCH_GRAD(0);
 #undef CNN_LAUNCH_GRAD
+#undef CNN_LAUNCH_GRAD3
   if (le != cudaSuccess) return cuda_fail(le, "k_grad_partials launch");
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch");
@@ -677,7 +706,7 @@ static int noalloc_scratch(float** rows) {
     float* ptr = nullptr;
     CNN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch));
     CNN_REQUIRE(ptr != nullptr, "cnn_grad_batch_noalloc: no device address for the scratch array");
-    CNN_CUDA(cudaFuncSetAttribute(k_grad_partials<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CNN_CUDA(cudaFuncSetAttribute(k_grad_partials<0, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)sizeof(TrSmem)));
     scratch_of_device[dev] = ptr;
   }
@@ -716,7 +745,7 @@ int cnn_grad_batch_noalloc(const float* d_params, const float* d_images, const u
   // by its block, padding included, so no row needs clearing.  The status word starts at zero when
   // the library is loaded, is only ever set by a wait that ran out, and stays set until
   // cnn_grad_batch_noalloc_status reads and clears it.
-  k_grad_partials<0, 1><<<grid, kTrThreads, sizeof(TrSmem), st>>>(d_images, d_labels, n, d_params, rows, status);
+  k_grad_partials<0, 1, false><<<grid, kTrThreads, sizeof(TrSmem), st>>>(d_images, d_labels, n, d_params, rows, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_grad_partials launch (no-alloc)");
   k_reduce_rows<<<(kNParamsPadded + 31) / 32, 32 * kRedGroups, 0, st>>>(rows, grid, d_grad, nullptr, 0.f, nullptr, 0.f);
