@@ -256,8 +256,8 @@ int cnn_dp_set_option(cnn_dp* dp, const char* key, int value) {
   return CNN_ERR_INVALID;
 }
 
-int cnn_dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels, long n_local, float scale,
-                float* d_grad_sum, float* d_mean_err, float err_scale, void* stream) {
+static int dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels, long n_local, float scale,
+                   float* d_grad_sum, float* d_mean_err, float err_scale, void* stream, bool chained) {
   CNN_REQUIRE(dp != nullptr, "cnn_dp_step: NULL handle");
   CNN_REQUIRE(dp->connected, "cnn_dp_step: cnn_dp_connect has not been called");
   CNN_REQUIRE(n_local >= 0, "cnn_dp_step: negative image count");
@@ -271,7 +271,7 @@ int cnn_dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels,
     CNN_REQUIRE((reinterpret_cast<uintptr_t>(d_images) & 15u) == 0,
                 "cnn_dp_step: image batch must start on a 16-byte boundary");
     grid = grid_for_batch(n_local);
-    if ((rc = launch_grad_partials(net, d_images, d_labels, n_local, grid, st)) != CNN_OK) return rc;
+    if ((rc = launch_grad_partials(net, d_images, d_labels, n_local, grid, st, chained)) != CNN_OK) return rc;
   }
   const long long wait_clocks = (long long)dp->wait_limit_ms * dp->clock_khz;
   const int send = dp->drop_next_send ? 0 : 1;
@@ -282,6 +282,11 @@ int cnn_dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels,
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "k_reduce_exchange_update launch");
   return CNN_OK;
+}
+
+int cnn_dp_step(cnn_dp* dp, const float* d_images, const unsigned int* d_labels, long n_local, float scale,
+                float* d_grad_sum, float* d_mean_err, float err_scale, void* stream) {
+  return dp_step(dp, d_images, d_labels, n_local, scale, d_grad_sum, d_mean_err, err_scale, stream, false);
 }
 
 int cnn_train_minibatch_dp(cnn_dp* dp, const float* d_images, const unsigned int* d_labels, long n,
@@ -297,8 +302,8 @@ int cnn_train_minibatch_dp(cnn_dp* dp, const float* d_images, const unsigned int
       const long size = (n - first) < global_batch ? (n - first) : global_batch;
       // this rank's contiguous slice of the global batch (sizes differ by at most one image)
       const long lo = size * dp->rank / dp->world, hi = size * (dp->rank + 1) / dp->world;
-      int rc = cnn_dp_step(dp, d_images + (first + lo) * kImg, d_labels + first + lo, hi - lo, dt / (float)size,
-                           nullptr, d_mean_err ? d_mean_err + e : nullptr, 1.0f / (float)n, stream);
+      int rc = dp_step(dp, d_images + (first + lo) * kImg, d_labels + first + lo, hi - lo, dt / (float)size,
+                       nullptr, d_mean_err ? d_mean_err + e : nullptr, 1.0f / (float)n, stream, first > 0 || e > 0);
       if (rc != CNN_OK) return rc;
     }
   }

@@ -166,8 +166,9 @@ __device__ __forceinline__ void thread_backward(const TrSmem& sm, const FwdRegs&
 
 // MINB = 1: one block per SM, no register cap -- lowest latency, used for small batches.
 // MINB = 2: two blocks per SM at 128 registers -- higher throughput on large batches.
-// EARLY = true (used when every block has one image: a training step of a few hundred images): the first
-// image copies are issued before the wait for the predecessor kernel.  With many images per block that order
+// EARLY = true (used when every block has one image -- a training step of a few hundred images -- and the
+// predecessor on the stream is this library's own reduce + update kernel of the previous step, which does
+// not touch the images): the first image copies are issued before the wait for the predecessor kernel.  With many images per block that order
 // of the prologue compiles to a slower loop (1.06 against 0.985 ms for 57,344 images), so it is a variant.
 template <int FAST, int MINB, bool EARLY>
 __global__ void __launch_bounds__(kTrThreads, MINB)
@@ -520,7 +521,7 @@ static int set_smem_attr(K kernel, size_t bytes) {
 }
 
 int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_labels, long n,
-                                int grid, cudaStream_t st) {
+                                int grid, cudaStream_t st, bool chained) {
   const size_t smem = sizeof(TrSmem);
   int rc;
   cudaError_t le = cudaSuccess;
@@ -532,7 +533,7 @@ int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_
   } while (0)
 #define CNN_LAUNCH_GRAD(FL)                                   \
   do {                                                        \
-    const bool early = ((long)grid == n);                     \
+    const bool early = chained && ((long)grid == n);          \
     if (grid > sm_count()) {                                  \
       if (early) CNN_LAUNCH_GRAD3(FL, 2, true);               \
       else CNN_LAUNCH_GRAD3(FL, 2, false);                    \
@@ -614,7 +615,7 @@ int cnn_train_minibatch(cnn_net* net, const float* d_images, const unsigned int*
     for (long first = 0; first < n; first += batch) {
       const long b = (n - first) < batch ? (n - first) : batch;
       const int grid = grid_for_batch(b);
-      if ((rc = launch_grad_partials(net, d_images + first * kImg, d_labels + first, b, grid, st)) != CNN_OK)
+      if ((rc = launch_grad_partials(net, d_images + first * kImg, d_labels + first, b, grid, st, first > 0 || e > 0)) != CNN_OK)
         return rc;
       cudaError_t err = launch_pdl(k_reduce_rows, dim3((kNParamsPadded + 31) / 32), dim3(32 * kRedGroups), 0, st,
                                    (const float*)net->d_partials, grid, net->d_grad, net->d_params, dt / (float)b,

@@ -118,8 +118,11 @@ int ensure_train_scratch(cnn_net* net, int rows);
 // Blocks of the minibatch gradient kernel for a batch of n images (one partial row per block).
 int grid_for_batch(long n);
 // Fused forward + backward of n images at fixed parameters: `grid` partial rows into net->d_partials.
+// `chained`: the kernel before this one on the stream is this library's reduce + update kernel of the previous
+// step of the same call (then, and only then, the gradient kernel may fetch its first images before waiting
+// for that kernel: see k_grad_partials).
 int launch_grad_partials(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int grid,
-                         cudaStream_t st);
+                         cudaStream_t st, bool chained = false);
 int launch_persample_cluster8(cnn_net* net, const float* d_images, const unsigned* d_labels, long n, int epochs,
                               float dt, float threshold, float* d_mean, int* d_ran, cudaStream_t st);
 
