@@ -31,7 +31,7 @@ namespace cnn {
 
 constexpr int kDpMaxRanks = 8;
 constexpr int kDpBlocks = (kNParamsPadded + 31) / 32;   // 74 blocks of 32 columns
-constexpr int kDpRedGroups = 16;   // row groups per column: 512 threads per block, at most ~19 dependent adds per thread
+constexpr int kDpRedGroups = 32;   // row groups per column: 1,024 threads per block, at most ~10 dependent adds per thread
 
 // Exchange buffer of one rank (device memory of that rank; every rank maps all of them).
 struct DpBuffer {
@@ -85,11 +85,11 @@ k_reduce_exchange_update(const float* __restrict__ rows, int n_rows, DpPeers pee
 
   float total;
   {
-    float q[4];
+    float q[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
       q[i] = (part[4 * i][lane] + part[4 * i + 1][lane]) + (part[4 * i + 2][lane] + part[4 * i + 3][lane]);
-    total = (q[0] + q[1]) + (q[2] + q[3]);
+    total = ((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]));
   }
   if (world == 1) {
     // a single rank has nobody to exchange with: reduce + update, no flags, no system-scope fences

@@ -330,11 +330,11 @@ k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ l
   if (tid < kRowStride - kNParams && kNParams + tid != kRowErr) row[kNParams + tid] = 0.f;
 }
 
-// G[i] = sum over rows (fixed order: sixteen interleaved row groups, then a fixed tree over the
+// G[i] = sum over rows (fixed order: thirty-two interleaved row groups, then a fixed tree over the
 // groups) and, if params is given, params[i] += scale * G[i].  Element kRowErr carries the error sum;
 // if mean_err is given, *mean_err += err_scale * that sum.  Block: 512 threads = 32 columns x 16 groups.
 // (The data-parallel exchange kernel adds a rank's rows in exactly this order.)
-constexpr int kRedGroups = 16;
+constexpr int kRedGroups = 32;
 
 __global__ void __launch_bounds__(32 * kRedGroups)
 k_reduce_rows(const float* __restrict__ rows, int n_rows, float* __restrict__ G,
@@ -352,11 +352,11 @@ k_reduce_rows(const float* __restrict__ rows, int n_rows, float* __restrict__ G,
   part[g][lane] = acc;
   __syncthreads();
   if (g == 0 && col < kRowStride) {
-    float q[4];
+    float q[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
       q[i] = (part[4 * i][lane] + part[4 * i + 1][lane]) + (part[4 * i + 2][lane] + part[4 * i + 3][lane]);
-    const float total = (q[0] + q[1]) + (q[2] + q[3]);
+    const float total = ((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]));
     if (G) G[col] = total;
     if (params && col < kNParams) params[col] = fmaf(scale, total, params[col]);
     if (mean_err && col == kRowErr) *mean_err += err_scale * total;
