@@ -332,7 +332,7 @@ k_grad_partials(const float* __restrict__ images, const unsigned* __restrict__ l
 
 // G[i] = sum over rows (fixed order: thirty-two interleaved row groups, then a fixed tree over the
 // groups) and, if params is given, params[i] += scale * G[i].  Element kRowErr carries the error sum;
-// if mean_err is given, *mean_err += err_scale * that sum.  Block: 512 threads = 32 columns x 16 groups.
+// if mean_err is given, *mean_err += err_scale * that sum.  Block: 1,024 threads = 32 columns x 32 groups.
 // (The data-parallel exchange kernel adds a rank's rows in exactly this order.)
 constexpr int kRedGroups = 32;
 
