@@ -6,20 +6,19 @@
 //   Gs[r][c] = sum over windows and maps of ds * a[4 wy + r][4 wx + c]           (bp_weight_s1)
 //
 // with A the im2col rows of the forward convolution, a the conv activations and ds the subsample
-// deltas.  The conv deltas never exist in HBM: the activations of a tile come in by TMA, four warps
+// deltas.  The conv deltas never exist in HBM: the activations of a tile come in by TMA, eight warps
 // turn them into deltas in shared memory (and add up the subsample-filter gradient on the way), and
 // the tensor core consumes them from there.
 // As an MMA:  D[M = F = 64][N = 32] += dcT[64][K = TP positions] * im2colT[32][K = TP positions], both
 // operands K-major (dcT with the 128-byte swizzle, im2colT in the canonical un-swizzled layout); tap
 // 25, unused by the filter, is a row of ones so that column 25 of D is the conv-bias gradient (taps
-// 26..31 are rows of zeros).  A tile is
-// TP consecutive positions of ONE image (the last tile of an image is ragged: the positions past
-// the image read as zeros).
+// 26..31 are rows of zeros).  A tile is TP consecutive positions of ONE image (the last tile of an
+// image is ragged: the positions past the image read as zeros).
 //
 // One CTA per SM, sixteen warps (128 registers each), four stages of 48 KB in shared memory:
-//   * the activation tile (64 maps x TP positions, 32 KB at TP = 128) comes in by TMA: activations are
-//     stored per (image, map) with positions contiguous, a 3-D tensor map (position, map, image) with a box of
-//     32 positions x 64 maps and the 128-byte swizzle writes one K-block of the operand (64 rows of
+//   * the activation tile (64 maps x TP positions, 32 KB at TP = 128) comes in by TMA: activations
+//     are stored per (image, map) with positions contiguous, a 3-D tensor map (position, map,
+//     image) with a box of 32 positions x 64 maps and the 128-byte swizzle writes one K-block of the operand (64 rows of
 //     128 bytes) per cp.async.bulk.tensor, and the MMA reads it through a SWIZZLE_128B descriptor.
 //     (Copying the tile with per-thread cp.async stalled at 2 TB/s: the copies of one tile took
 //     4,000 cycles to get into the load/store pipeline.)  No multicast; positions past the image
